@@ -1,0 +1,69 @@
+// Host-visible description of one launch of the tcgen05 GEMM kernel.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace gcb {
+
+enum OutKind : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_S32 = 2, OUT_DEQUANT_F32 = 3 };
+enum BiasKind : int { BIAS_NONE = 0, BIAS_BF16 = 1, BIAS_F32 = 2 };
+enum ErrCode : int {
+  ERR_NONE = 0,
+  ERR_WAIT_EMPTY = 1,      // producer: a pipeline stage was never released
+  ERR_WAIT_FULL = 2,       // MMA: a stage's TMA bytes never arrived
+  ERR_WAIT_TMEM_EMPTY = 3, // MMA: an accumulator was never drained
+  ERR_WAIT_TMEM_FULL = 4,  // epilogue: an accumulator was never committed
+  ERR_WAIT_DRAIN = 5,      // tear-down: an issued copy did not land
+};
+
+// Geometry of one operand's pipeline stage in shared memory and of the
+// descriptors that walk it.
+struct OperandGeom {
+  uint32_t mn_major;   // 0: K contiguous in memory, 1: MN contiguous
+  uint32_t boxes;      // TMA boxes per stage
+  uint32_t box_bytes;  // bytes per box
+  uint32_t box_mn;     // MN elements covered by one box (MN-major only)
+  uint32_t lbo, sbo;   // descriptor leading / stride byte offsets
+  uint32_t kstep;      // bytes to advance the start address per MMA K step
+  uint32_t bytes;      // bytes per stage
+};
+
+struct GemmParams {
+  // D[Mm x Nm] = A[Mm x K] . B[Nm x K]^T in MMA orientation (for the swapped
+  // orientation Mm indexes output columns and Nm output rows).
+  int Mm, Nm, K;
+  int BN;               // MMA N of one tile (multiple of 16, <= 256)
+  int tiles_m, tiles_n; // tile grid in MMA orientation
+  int k_blocks;         // K blocks of BK elements over the whole K
+  int splits;           // split-K factor (1 = none)
+  int bk_elems;         // elements per K block (128 bytes worth)
+  int stages;
+  int group_m;          // rasterisation: tiles_m rows walked per column sweep
+  OperandGeom a, b;
+  uint32_t idesc;
+  uint32_t tmem_cols;   // allocated TMEM columns (power of two >= 2*BN, >= 32)
+  // epilogue
+  int out_kind;
+  void *out;            // [rows x ld_out]
+  long long ld_out;     // elements
+  long long split_stride; // elements between split-K partial planes (out_kind F32/S32 only)
+  int bias_kind;
+  const void *bias;     // indexed by output column
+  const float *scale;   // OUT_DEQUANT_F32: per output column
+  const int32_t *comp;  // OUT_DEQUANT_F32: per output column, subtracted from the accumulator
+  int32_t *acc_dump;    // optional raw s32 accumulators [rows x ld_dump]
+  long long ld_dump;
+  int relu;
+  int out_rows, out_cols; // logical output extent (for edge predication)
+  int *error;           // device int, set to an ErrCode on a bounded-wait time-out
+};
+
+// KIND: 0 = bf16 x bf16 -> f32, 1 = u8 x s8 -> s32.  SWAPPED: MMA rows are output columns.
+template <int KIND, bool SWAPPED>
+cudaError_t launch_gemm_kernel(const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p, int grid,
+                               size_t smem, cudaStream_t stream);
+
+size_t gemm_smem_bytes(const GemmParams &p);
+
+} // namespace gcb

@@ -1,0 +1,474 @@
+// CUDA runtime: device state, tensor maps, tile selection, matmul launch
+// planning and the small helper kernels (split-K reduction + epilogue, int8
+// column sums, exact-order SIMT matmul).
+#include "runtime.h"
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "sm100_ptx.cuh"
+
+namespace gcb {
+
+// ----------------------------------------------------------------------------- device state
+static std::mutex g_dev_mutex;
+static DeviceState g_devs[64];
+
+DeviceState &device_state() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) throw CudaError(std::string("no CUDA device: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) throw CudaError("device ordinal out of range");
+  std::lock_guard<std::mutex> g(g_dev_mutex);
+  DeviceState &d = g_devs[dev];
+  if (d.device < 0) {
+    cudaDeviceProp prop;
+    GCB_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      throw CudaError("this library is built for sm_100a only; device is sm_" + std::to_string(prop.major) +
+                      std::to_string(prop.minor));
+    d.sm_count = prop.multiProcessorCount;
+    GCB_CUDA(cudaMalloc(&d.d_error, sizeof(int)));
+    GCB_CUDA(cudaMemset(d.d_error, 0, sizeof(int)));
+    d.device = dev;
+  }
+  return d;
+}
+
+void *DeviceState::ensure_workspace(size_t bytes) {
+  if (bytes <= workspace_bytes) return workspace;
+  GCB_CUDA(cudaDeviceSynchronize());
+  if (workspace) GCB_CUDA(cudaFree(workspace));
+  workspace = nullptr;
+  workspace_bytes = 0;
+  size_t want = std::max(bytes, size_t(64) << 20);
+  GCB_CUDA(cudaMalloc(&workspace, want));
+  workspace_bytes = want;
+  return workspace;
+}
+
+int read_device_error(cudaStream_t stream) {
+  DeviceState &d = device_state();
+  int h = 0;
+  GCB_CUDA(cudaMemcpyAsync(&h, d.d_error, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  GCB_CUDA(cudaStreamSynchronize(stream));
+  if (h != 0) GCB_CUDA(cudaMemsetAsync(d.d_error, 0, sizeof(int), stream));
+  return h;
+}
+
+// ----------------------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  if (!fn) throw CudaError("cuTensorMapEncodeTiled is not available from the driver");
+  return fn;
+}
+
+CUtensorMap make_tmap_2d(ElemType t, const void *ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                         uint32_t box_inner, uint32_t box_outer) {
+  CUtensorMap m;
+  CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  switch (t) {
+  case ElemType::BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+  case ElemType::U8:
+  case ElemType::S8: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+  case ElemType::F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+  case ElemType::S32: dt = CU_TENSOR_MAP_DATA_TYPE_INT32; break;
+  }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(&m, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw CudaError("cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)));
+  return m;
+}
+
+bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes) {
+  return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && ((row_elems * elem_bytes) & 15) == 0;
+}
+
+// ----------------------------------------------------------------------------- tile selection
+static int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); }
+
+MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count) {
+  MatmulConfig c{};
+  const int bk = 128 / dtype_bytes;
+  const int k_blocks = ceil_div(K, bk);
+  const int out_gran = out_bytes == 2 ? 64 : 32; // epilogue works in 128-byte row slabs
+  c.swapped = (M <= 64 && N >= 128) ? 1 : 0;
+  int tiles;
+  if (c.swapped) {
+    c.bn = std::max(16, ceil_div(M, 16) * 16);
+    tiles = ceil_div(N, 128);
+  } else {
+    // Largest tile whose wave quantisation loses least; ties go to the larger
+    // tile (more operand reuse per byte staged in shared memory).
+    const int cand[3] = {256, 128, 64};
+    double best = -1.0;
+    int best_bn = 256;
+    for (int bn : cand) {
+      if (bn % out_gran) continue;
+      int bn_eff = bn;
+      if (N < bn) bn_eff = std::max(out_gran, ceil_div(N, out_gran) * out_gran);
+      const int t = ceil_div(M, 128) * ceil_div(N, bn_eff);
+      const int waves = ceil_div(t, sm_count);
+      const double useful = double(M) * double(N) / (double(waves) * sm_count * 128.0 * bn_eff);
+      const double reuse = bn_eff >= 256 ? 1.0 : (bn_eff >= 128 ? 0.88 : 0.70);
+      const double score = useful * reuse;
+      if (score > best + 1e-9) { best = score; best_bn = bn_eff; }
+    }
+    c.bn = best_bn;
+    tiles = ceil_div(M, 128) * ceil_div(N, c.bn);
+  }
+  // split-K only when the tile grid leaves most SMs idle and K is deep
+  c.splits = 1;
+  if (tiles * 2 <= sm_count && k_blocks >= 16) {
+    int s = std::min({sm_count / tiles, k_blocks / 8, 32});
+    if (c.swapped) s = std::min({(2 * sm_count + tiles - 1) / tiles, k_blocks / 8, 32});
+    c.splits = std::max(1, s);
+  } else if (c.swapped && k_blocks >= 16) {
+    // decode shapes stream the weights once: keep every SM busy with >= 2 units
+    int s = std::min({(3 * sm_count + tiles - 1) / tiles, k_blocks / 8, 32});
+    c.splits = std::max(1, s);
+  }
+  // every split must own at least one K block
+  {
+    const int per = ceil_div(k_blocks, c.splits);
+    c.splits = ceil_div(k_blocks, per);
+  }
+  const size_t a_bytes = 128 * 128;
+  size_t b_bytes;
+  {
+    // worst case over orientations: MN-major operands are staged in full 128-byte boxes
+    const int box_mn = 128 / dtype_bytes;
+    const size_t mn = size_t(ceil_div(c.bn, box_mn)) * size_t(bk) * 128;
+    const size_t km = size_t(c.bn) * 128;
+    b_bytes = std::max(mn, km);
+  }
+  const size_t budget = 232448 - 1024 - 4 * 4096 - 256;
+  c.stages = int(std::min<size_t>(8, budget / (a_bytes + b_bytes)));
+  c.stages = std::max(2, std::min(c.stages, std::max(2, k_blocks)));
+  c.group_m = 8;
+  c.grid = std::min(tiles * c.splits, sm_count);
+  if (const char *ov = std::getenv("GC_B200_TILE")) {
+    // "bn,splits,stages,group_m" — any field may be 0 to keep the heuristic's choice
+    int bn = 0, sp = 0, st = 0, gm = 0;
+    if (std::sscanf(ov, "%d,%d,%d,%d", &bn, &sp, &st, &gm) >= 1) {
+      if (bn > 0 && !c.swapped) c.bn = bn;
+      if (sp > 0) { const int per = ceil_div(k_blocks, sp); c.splits = ceil_div(k_blocks, per); }
+      if (st > 0) c.stages = std::min(st, c.stages);
+      if (gm > 0) c.group_m = gm;
+      const int t2 = c.swapped ? ceil_div(N, 128) : ceil_div(M, 128) * ceil_div(N, c.bn);
+      c.grid = std::min(t2 * c.splits, sm_count);
+    }
+  }
+  return c;
+}
+
+// ----------------------------------------------------------------------------- matmul planning
+static OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes) {
+  OperandGeom g{};
+  const uint32_t bk = 128 / elem_bytes;  // K elements per stage
+  g.mn_major = mn_major ? 1u : 0u;
+  if (!mn_major) {
+    g.boxes = 1;
+    g.box_bytes = uint32_t(tile_mn) * 128u;
+    g.box_mn = uint32_t(tile_mn);
+    g.lbo = 16;
+    g.sbo = 1024;
+    g.kstep = 32;
+    g.bytes = g.box_bytes;
+  } else {
+    g.box_mn = 128 / elem_bytes;
+    g.boxes = (uint32_t(tile_mn) + g.box_mn - 1) / g.box_mn;
+    g.box_bytes = bk * 128u;
+    g.lbo = g.box_bytes;
+    g.sbo = 1024;
+    g.kstep = (32u / elem_bytes) * 128u;
+    g.bytes = g.boxes * g.box_bytes;
+  }
+  return g;
+}
+
+static CUtensorMap operand_tmap(const OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
+                                int64_t k_total, int tile_mn) {
+  const uint32_t bk = 128 / elem_bytes;
+  if (!g.mn_major)  // memory [mn_total][k_total], K contiguous
+    return make_tmap_2d(t, ptr, uint64_t(k_total), uint64_t(mn_total), uint64_t(k_total) * elem_bytes, bk,
+                        uint32_t(tile_mn));
+  // memory [k_total][mn_total], MN contiguous
+  return make_tmap_2d(t, ptr, uint64_t(mn_total), uint64_t(k_total), uint64_t(mn_total) * elem_bytes, g.box_mn, bk);
+}
+
+void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
+  DeviceState &dev = device_state();
+  const int eb = a.int8 ? 1 : 2;
+  const int out_bytes = a.out_kind == OUT_BF16 ? 2 : 4;
+  MatmulConfig cfg = a.force ? *a.force : select_matmul_config(a.M, a.N, a.K, eb, out_bytes, dev.sm_count);
+  const int64_t ld_out = a.ld_out ? a.ld_out : a.N;
+
+  GemmParams p{};
+  p.K = int(a.K);
+  p.bk_elems = 128 / eb;
+  p.k_blocks = ceil_div(a.K, p.bk_elems);
+  p.splits = cfg.splits;
+  p.stages = cfg.stages;
+  p.group_m = cfg.group_m;
+  p.BN = cfg.bn;
+  p.out_rows = int(a.M);
+  p.out_cols = int(a.N);
+  p.error = dev.d_error;
+
+  // operand roles in MMA orientation
+  const void *pa, *pb;
+  bool a_mn, b_mn;
+  int64_t mn_a, mn_b;
+  ElemType ta, tb;
+  uint32_t fa, fb;
+  if (!cfg.swapped) {
+    pa = a.A; a_mn = a.trans_a != 0; mn_a = a.M;
+    pb = a.B; b_mn = a.trans_b == 0; mn_b = a.N;
+    ta = a.int8 ? ElemType::U8 : ElemType::BF16; tb = a.int8 ? ElemType::S8 : ElemType::BF16;
+    fa = a.int8 ? 0u : 1u; fb = 1u;
+  } else {
+    pa = a.B; a_mn = a.trans_b == 0; mn_a = a.N;
+    pb = a.A; b_mn = a.trans_a != 0; mn_b = a.M;
+    ta = a.int8 ? ElemType::S8 : ElemType::BF16; tb = a.int8 ? ElemType::U8 : ElemType::BF16;
+    fa = 1u; fb = a.int8 ? 0u : 1u;
+  }
+  p.Mm = int(mn_a);
+  p.Nm = int(mn_b);
+  p.tiles_m = ceil_div(mn_a, 128);
+  p.tiles_n = ceil_div(mn_b, p.BN);
+  p.a = operand_geom(a_mn, 128, eb);
+  p.b = operand_geom(b_mn, p.BN, eb);
+  p.idesc = umma_instr_desc(a.int8 ? 2u : 1u, fa, fb, a_mn ? 1u : 0u, b_mn ? 1u : 0u, 128u, uint32_t(p.BN));
+  uint32_t cols = 32;
+  while (cols < uint32_t(2 * p.BN)) cols <<= 1;
+  p.tmem_cols = cols;
+
+  const CUtensorMap tmA = operand_tmap(p.a, ta, eb, pa, mn_a, a.K, 128);
+  const CUtensorMap tmB = operand_tmap(p.b, tb, eb, pb, mn_b, a.K, p.BN);
+
+  const bool split = cfg.splits > 1;
+  void *planes = nullptr;
+  if (split) {
+    const size_t need = size_t(cfg.splits) * size_t(a.M) * size_t(a.N) * 4;
+    if (a.scratch) {
+      if (a.scratch_bytes < need) throw std::invalid_argument("split-K scratch too small");
+      planes = a.scratch;
+    } else {
+      planes = dev.ensure_workspace(need);
+    }
+    p.out_kind = a.int8 ? OUT_S32 : OUT_F32;
+    p.out = planes;
+    p.ld_out = a.N;
+    p.split_stride = a.M * a.N;
+    p.bias_kind = BIAS_NONE;
+    p.relu = 0;
+  } else {
+    p.out_kind = a.out_kind;
+    p.out = a.out;
+    p.ld_out = ld_out;
+    p.split_stride = 0;
+    p.bias_kind = a.bias_kind;
+    p.bias = a.bias;
+    p.scale = a.scale;
+    p.comp = a.comp;
+    p.acc_dump = a.acc_dump;
+    p.ld_dump = a.N;
+    p.relu = a.relu;
+  }
+  const int units = p.tiles_m * p.tiles_n * p.splits;
+  const int grid = std::max(1, std::min(units, cfg.grid > 0 ? cfg.grid : dev.sm_count));
+  const size_t smem = gemm_smem_bytes(p);
+  if (smem > 232448) throw std::invalid_argument("matmul tile configuration exceeds shared memory");
+  cudaError_t e;
+  if (!a.int8) e = cfg.swapped ? launch_gemm_kernel<0, true>(tmA, tmB, p, grid, smem, stream)
+                               : launch_gemm_kernel<0, false>(tmA, tmB, p, grid, smem, stream);
+  else         e = cfg.swapped ? launch_gemm_kernel<1, true>(tmA, tmB, p, grid, smem, stream)
+                               : launch_gemm_kernel<1, false>(tmA, tmB, p, grid, smem, stream);
+  if (e != cudaSuccess) throw CudaError(std::string("gemm launch: ") + cudaGetErrorString(e));
+  if (split) {
+    if (ld_out != a.N) throw std::invalid_argument("split-K with a strided output is not supported");
+    reduce_planes(planes, cfg.splits, a.M * a.N, a.out, a.M, a.N, a.out_kind, a.bias_kind, a.bias, a.scale, a.comp,
+                  a.acc_dump, a.relu, stream);
+  }
+}
+
+// ----------------------------------------------------------------------------- helper kernels
+// Sum split-K planes in split order (deterministic) and apply the epilogue.
+template <bool INT>
+__global__ void reduce_planes_kernel(const void *parts, int nparts, long long plane, void *out, long long M,
+                                     long long N, int out_kind, int bias_kind, const void *bias, const float *scale,
+                                     const int32_t *comp, int32_t *acc_dump, int relu) {
+  const long long total = M * N;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int col = int(i % N);
+    if (INT) {
+      const int32_t *p = reinterpret_cast<const int32_t *>(parts);
+      int32_t s = p[i];
+      for (int k = 1; k < nparts; ++k) s += p[(long long)k * plane + i];
+      if (acc_dump) acc_dump[i] = s;
+      if (out_kind == OUT_S32) {
+        reinterpret_cast<int32_t *>(out)[i] = s;
+      } else {
+        float f = __fmul_rn(float(s - (comp ? comp[col] : 0)), scale[col]);
+        if (bias_kind == BIAS_F32) f = __fadd_rn(f, reinterpret_cast<const float *>(bias)[col]);
+        if (relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
+        reinterpret_cast<float *>(out)[i] = f;
+      }
+    } else {
+      const float *p = reinterpret_cast<const float *>(parts);
+      float s = p[i];
+      for (int k = 1; k < nparts; ++k) s = __fadd_rn(s, p[(long long)k * plane + i]);
+      if (out_kind == OUT_F32) {
+        if (bias_kind == BIAS_F32) s = __fadd_rn(s, reinterpret_cast<const float *>(bias)[col]);
+        if (relu) s = (s != s) ? s : (s > 0.f ? s : 0.f);
+        reinterpret_cast<float *>(out)[i] = s;
+      } else {
+        uint32_t y = f32_to_bf16_bits(s);
+        if (bias_kind == BIAS_BF16) {
+          const uint32_t b = reinterpret_cast<const uint16_t *>(bias)[col];
+          y = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(y), bf16_bits_to_f32(b)));
+        }
+        if (relu) { const float f = bf16_bits_to_f32(y); y = (f != f) ? y : (f > 0.f ? y : 0u); }
+        reinterpret_cast<uint16_t *>(out)[i] = uint16_t(y);
+      }
+    }
+  }
+}
+
+void reduce_planes(const void *parts, int nparts, int64_t plane, void *out, int64_t M, int64_t N, int out_kind,
+                   int bias_kind, const void *bias, const float *scale, const int32_t *comp, int32_t *acc_dump,
+                   int relu, cudaStream_t stream) {
+  DeviceState &dev = device_state();
+  const long long total = M * N;
+  const int threads = 256;
+  const int blocks = int(std::min<long long>((total + threads - 1) / threads, (long long)dev.sm_count * 8));
+  const bool is_int = (out_kind == OUT_S32 || out_kind == OUT_DEQUANT_F32);
+  if (is_int)
+    reduce_planes_kernel<true><<<blocks, threads, 0, stream>>>(parts, nparts, plane, out, M, N, out_kind, bias_kind,
+                                                              bias, scale, comp, acc_dump, relu);
+  else
+    reduce_planes_kernel<false><<<blocks, threads, 0, stream>>>(parts, nparts, plane, out, M, N, out_kind, bias_kind,
+                                                               bias, scale, comp, acc_dump, relu);
+  GCB_CUDA(cudaGetLastError());
+}
+
+void reduce_epilogue_bf16(const float *parts, int nparts, int64_t plane, const void *bias_bf16, void *out_bf16,
+                          int64_t M, int64_t N, int relu, cudaStream_t stream) {
+  reduce_planes(parts, nparts, plane, out_bf16, M, N, OUT_BF16, bias_bf16 ? BIAS_BF16 : BIAS_NONE, bias_bf16, nullptr,
+                nullptr, nullptr, relu, stream);
+}
+
+// comp[n] = zp * sum_k W[k][n].  One thread per column, rows strided over
+// blockIdx.y with an exact integer atomic combine.
+__global__ void colsum_s8_kernel(const int8_t *W, int32_t *comp, long long K, long long N, int32_t zp) {
+  const long long n = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  int32_t s = 0;
+  for (long long k = blockIdx.y; k < K; k += gridDim.y) s += int32_t(W[k * N + n]);
+  atomicAdd(&comp[n], s * zp);
+}
+
+void colsum_s8(const int8_t *W, int32_t *comp, int64_t K, int64_t N, int32_t zp, cudaStream_t stream) {
+  GCB_CUDA(cudaMemsetAsync(comp, 0, size_t(N) * 4, stream));
+  dim3 grid(unsigned((N + 255) / 256), unsigned(std::min<int64_t>(K, 64)));
+  colsum_s8_kernel<<<grid, 256, 0, stream>>>(W, comp, K, N, zp);
+  GCB_CUDA(cudaGetLastError());
+}
+
+// Exact-order SIMT matmul: every output element accumulates k ascending with a
+// separate multiply and add, the arithmetic of the reference's scalar loops
+// (BrgemmNaive.cpp:46-99).  64x64 output tile, 16-deep K slabs in shared memory.
+template <int IN_KIND>
+__global__ void __launch_bounds__(256) matmul_simt_kernel(const void *Ap, const void *Bp, const void *biasp, void *outp,
+                                                         int M, int N, int K, int ta, int tb, int relu) {
+  __shared__ float As[16][65];
+  __shared__ float Bs[16][65];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  auto ld = [&](const void *base, long long idx) -> float {
+    if (IN_KIND == 0) return reinterpret_cast<const float *>(base)[idx];
+    return bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(base)[idx]);
+  };
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int e = threadIdx.x; e < 16 * 64; e += 256) {
+      const int kk = e / 64, mm = e % 64;
+      const int k = k0 + kk;
+      float av = 0.f, bv = 0.f;
+      if (k < K && m0 + mm < M) av = ta ? ld(Ap, (long long)k * M + (m0 + mm)) : ld(Ap, (long long)(m0 + mm) * K + k);
+      if (k < K && n0 + mm < N) bv = tb ? ld(Bp, (long long)(n0 + mm) * K + k) : ld(Bp, (long long)k * N + (n0 + mm));
+      As[kk][mm] = av;
+      Bs[kk][mm] = bv;
+    }
+    __syncthreads();
+    const int klim = min(16, K - k0);
+    for (int kk = 0; kk < klim; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], b[j]));
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m >= M || n >= N) continue;
+      if (IN_KIND == 0) {
+        float v = acc[i][j];
+        if (biasp) v = __fadd_rn(v, reinterpret_cast<const float *>(biasp)[n]);
+        if (relu) v = (v != v) ? v : (v > 0.f ? v : 0.f);
+        reinterpret_cast<float *>(outp)[(long long)m * N + n] = v;
+      } else {
+        uint32_t y = f32_to_bf16_bits(acc[i][j]);
+        if (biasp)
+          y = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(y), bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(biasp)[n])));
+        if (relu) { const float f = bf16_bits_to_f32(y); y = (f != f) ? y : (f > 0.f ? y : 0u); }
+        reinterpret_cast<uint16_t *>(outp)[(long long)m * N + n] = uint16_t(y);
+      }
+    }
+}
+
+void matmul_simt(const void *A, const void *B, const void *bias, void *out, int64_t M, int64_t N, int64_t K,
+                 int trans_a, int trans_b, int in_kind, int relu, cudaStream_t stream) {
+  device_state();
+  dim3 grid(unsigned((N + 63) / 64), unsigned((M + 63) / 64));
+  if (in_kind == 0)
+    matmul_simt_kernel<0><<<grid, 256, 0, stream>>>(A, B, bias, out, int(M), int(N), int(K), trans_a, trans_b, relu);
+  else
+    matmul_simt_kernel<1><<<grid, 256, 0, stream>>>(A, B, bias, out, int(M), int(N), int(K), trans_a, trans_b, relu);
+  GCB_CUDA(cudaGetLastError());
+}
+
+} // namespace gcb

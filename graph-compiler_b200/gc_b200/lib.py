@@ -1,0 +1,179 @@
+"""ctypes binding of libGcDnnlApi.so — the only way Python reaches the CUDA kernels.
+
+There is no fallback: if the shared library is missing, or a launcher reports
+that no sm_100 device is usable, an exception is raised.  torch is used here
+only for device memory (``tensor.data_ptr()``) and the current stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libGcDnnlApi.so")
+
+_i64, _u64, _i32, _int, _vp, _f32 = C.c_int64, C.c_uint64, C.c_int32, C.c_int, C.c_void_p, C.c_float
+
+
+class GcB200Error(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"gc_b200 status {status}: {msg}")
+        self.status = status
+
+
+class MatmulConfig(C.Structure):
+    """Mirror of ``gcb200_matmul_config``."""
+
+    _fields_ = [("swapped", _int), ("bn", _int), ("splits", _int), ("stages", _int), ("group_m", _int), ("grid", _int)]
+
+    def __repr__(self):
+        return (f"MatmulConfig(swapped={self.swapped}, bn={self.bn}, splits={self.splits}, stages={self.stages}, "
+                f"group_m={self.group_m}, grid={self.grid})")
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `python graph-compiler_b200/build.py` (there is no CPU fallback)")
+    lib = C.CDLL(LIB_PATH)
+    lib.gcb200_last_error.restype = C.c_char_p
+    sig = {
+        "gcb200_device_error": [_vp, C.POINTER(_int)],
+        "gcb200_sm_count": [C.POINTER(_int)],
+        "gcb200_matmul_bf16": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
+        "gcb200_matmul_bf16_cfg": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig), _vp],
+        "gcb200_matmul_bf16_f32out": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
+        "gcb200_reduce_bias_act_bf16": [_vp, _int, _i64, _vp, _vp, _i64, _i64, _int, _vp],
+        "gcb200_matmul_u8s8": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
+        "gcb200_colsum_s8": [_vp, _vp, _i64, _i64, _i32, _vp],
+        "gcb200_matmul_f32": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
+        "gcb200_select_matmul_config": [_i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig)],
+    }
+    for name, argtypes in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _int
+    lib.dnnl_brgemm_dispatch.restype = _i64
+    lib.dnnl_brgemm_dispatch.argtypes = [_i64] * 8 + [_f32, _i64, _i64]
+    lib.dnnl_brgemm_tileconfig.restype = None
+    lib.dnnl_brgemm_tileconfig.argtypes = [_i64]
+    lib.dnnl_brgemm_tilerelease.restype = None
+    lib.dnnl_brgemm_execute.restype = None
+    lib.dnnl_brgemm_execute.argtypes = [_i64, _vp, _u64, _vp, _u64, _vp, _u64, _int]
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise GcB200Error(status, load().gcb200_last_error().decode(errors="replace"))
+
+
+def _ptr(t):
+    return None if t is None else _vp(t.data_ptr())
+
+
+def _stream():
+    import torch
+
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def sm_count() -> int:
+    n = _int(0)
+    check(load().gcb200_sm_count(C.byref(n)))
+    return n.value
+
+
+def device_error() -> int:
+    code = _int(0)
+    check(load().gcb200_device_error(_stream(), C.byref(code)))
+    return code.value
+
+
+def select_matmul_config(M, N, K, dtype_bytes=2, out_bytes=2, sms=148) -> MatmulConfig:
+    cfg = MatmulConfig()
+    check(load().gcb200_select_matmul_config(M, N, K, dtype_bytes, out_bytes, sms, C.byref(cfg)))
+    return cfg
+
+
+# ----------------------------------------------------------------------------- launchers on torch CUDA tensors
+def matmul_bf16(A, B, bias=None, relu=False, transpose_a=False, transpose_b=False, out=None, cfg: MatmulConfig | None = None):
+    """Y = act(bf16(bf16(op(A).op(B)) + bias)) on bf16 CUDA tensors."""
+    import torch
+
+    assert A.is_cuda and A.dtype == torch.bfloat16 and A.is_contiguous() and B.is_contiguous()
+    K, M = (A.shape if transpose_a else A.shape[::-1])
+    N = B.shape[0] if transpose_b else B.shape[1]
+    assert (B.shape[1] if transpose_b else B.shape[0]) == K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    if cfg is None:
+        check(load().gcb200_matmul_bf16(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), M, N, K, int(transpose_a),
+                                        int(transpose_b), int(relu), _stream()))
+    else:
+        check(load().gcb200_matmul_bf16_cfg(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), M, N, K, int(transpose_a),
+                                            int(transpose_b), int(relu), C.byref(cfg), _stream()))
+    return out
+
+
+def matmul_bf16_f32out(A, B, transpose_a=False, transpose_b=False, out=None):
+    import torch
+
+    K, M = (A.shape if transpose_a else A.shape[::-1])
+    N = B.shape[0] if transpose_b else B.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    check(load().gcb200_matmul_bf16_f32out(_ptr(A), _ptr(B), _ptr(out), M, N, K, int(transpose_a), int(transpose_b),
+                                           _stream()))
+    return out
+
+
+def reduce_bias_act_bf16(parts, bias=None, relu=False, out=None):
+    """parts: f32 [nparts, M, N] contiguous."""
+    import torch
+
+    nparts, M, N = parts.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=parts.device)
+    check(load().gcb200_reduce_bias_act_bf16(_ptr(parts), nparts, M * N, _ptr(bias), _ptr(out), M, N, int(relu), _stream()))
+    return out
+
+
+def colsum_s8(W, zp_a: int):
+    import torch
+
+    K, N = W.shape
+    comp = torch.empty((N,), dtype=torch.int32, device=W.device)
+    check(load().gcb200_colsum_s8(_ptr(W), _ptr(comp), K, N, zp_a, _stream()))
+    return comp
+
+
+def matmul_u8s8(A, W, scale=None, bias=None, comp=None, want_acc=False):
+    """Returns (out f32 or None, acc s32 or None)."""
+    import torch
+
+    M, K = A.shape
+    N = W.shape[1]
+    out = torch.empty((M, N), dtype=torch.float32, device=A.device) if scale is not None else None
+    acc = torch.empty((M, N), dtype=torch.int32, device=A.device) if (want_acc or out is None) else None
+    check(load().gcb200_matmul_u8s8(_ptr(A), _ptr(W), _ptr(scale), _ptr(bias), _ptr(comp), _ptr(out), _ptr(acc), M, N, K,
+                                    _stream()))
+    return out, acc
+
+
+def matmul_f32(A, B, bias=None, relu=False, transpose_a=False, transpose_b=False):
+    import torch
+
+    K, M = (A.shape if transpose_a else A.shape[::-1])
+    N = B.shape[0] if transpose_b else B.shape[1]
+    out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    check(load().gcb200_matmul_f32(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), M, N, K, int(transpose_a), int(transpose_b),
+                                   int(relu), _stream()))
+    return out

@@ -1,0 +1,131 @@
+/*
+ * gc_b200.h — C ABI of the B200 (sm_100a) execution backend for Intel Graph
+ * Compiler's matmul / MLP / attention partitions.
+ *
+ * Two groups of entry points live in libGcDnnlApi.so:
+ *   1. the oneDNN-graph backend API of the reference (dnnl_graph_compiler.h in
+ *      this directory) — create / compile / execute on JSON partitions;
+ *   2. the entry points below: the runtime symbols the reference's JIT-ed code
+ *      calls (dnnl_brgemm_*), and direct launchers for the kernels that replace
+ *      its deep-tiled matmul pipeline, for callers that already hold device
+ *      buffers (benchmark harnesses, a framework's own executor).
+ *
+ * All pointers are plain device pointers unless stated otherwise; `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).  Every
+ * function returns 0 on success or a gcb200_status; the message of the last
+ * failure on the calling thread is available from gcb200_last_error().
+ * Nothing here falls back to the CPU: without a usable sm_100 device every
+ * launcher fails with GCB200_NO_DEVICE.
+ */
+#ifndef GC_B200_H
+#define GC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  GCB200_OK = 0,
+  GCB200_INVALID_ARGUMENT = 1,
+  GCB200_UNIMPLEMENTED = 2,
+  GCB200_NO_DEVICE = 3,
+  GCB200_CUDA_ERROR = 4,
+  GCB200_DEVICE_TIMEOUT = 5 /* a bounded wait inside a kernel ran out; see gcb200_device_error */
+} gcb200_status;
+
+const char *gcb200_last_error(void);
+
+/* Reads and clears the device-side error word (0 = none; otherwise the code of
+ * the bounded wait that gave up).  Synchronises `stream`. */
+int gcb200_device_error(void *stream, int *code);
+
+/* Number of SMs of the current device (persistent grids are sized from it). */
+int gcb200_sm_count(int *count);
+
+/* ---------------------------------------------------------------------------
+ * bf16 matmul with fused post-ops.
+ * Replaces: onednn_graph.matmul lowered by MatMulOpLowering
+ * (lib/gc/Transforms/OneDNNGraphToLinalg.cpp:421-499), deep-tiled by
+ * DeepTileMatmul (lib/gc/Transforms/DeepTileContractionOp.cpp:958-1014) into
+ * brgemm calls (lib/gc/ExecutionEngine/CPURuntime/Microkernel/BrgemmOnednn.cpp:
+ * 145-168) with the bias add and ReLU fused by IterativeTilingAndFusion.cpp:743-828.
+ *
+ *   Y = act( bf16( bf16(op(A) . op(B)) + bias ) )      f32 accumulation
+ * A: [M,K] (or [K,M] when transpose_a); B: [K,N] (or [N,K] when transpose_b);
+ * bias: [N] bf16 or NULL; Y: [M,N] bf16, all row-major and contiguous.
+ */
+int gcb200_matmul_bf16(const void *A, const void *B, const void *bias, void *Y, int64_t M, int64_t N, int64_t K,
+                       int transpose_a, int transpose_b, int relu, void *stream);
+
+/* Same contraction, raw f32 accumulators out (no rounding, no post-op): the
+ * K-split form of the reference, where partial sums stay f32 until they are
+ * reduced (DeepTileContractionOp.cpp:446-471, 988-996).  Used by row-parallel
+ * layers whose partial sums are reduced across GPUs. */
+int gcb200_matmul_bf16_f32out(const void *A, const void *B, float *Y, int64_t M, int64_t N, int64_t K,
+                              int transpose_a, int transpose_b, void *stream);
+
+/* Sum `nparts` f32 planes [M,N] (`plane_stride` elements apart) in plane order,
+ * then apply the bf16 epilogue bf16(bf16(sum)+bias), ReLU.  The reduce + cast
+ * step of the K-split form (DeepTileContractionOp.cpp:446-471). */
+int gcb200_reduce_bias_act_bf16(const float *parts, int nparts, int64_t plane_stride, const void *bias, void *Y,
+                                int64_t M, int64_t N, int relu, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * u8 x s8 -> s32 matmul with zero-point compensation and per-channel dequant.
+ * Replaces: the int8 brgemm path (BrgemmNaive.cpp:102-140 semantics; dtype
+ * pairs lib/gc/Dialect/Microkernel/MicrokernelOps.cpp:556-570) with the
+ * compensation of legacy/core/src/ops/matmul_core.cpp:655-700.
+ *
+ *   acc = A_u8 . W_s8  (exact s32);  comp[n] = zp_a * sum_k W[k,n]
+ *   out = float(acc - comp[n]) * scale[n] + bias[n]
+ * A: [M,K] u8; W: [K,N] s8; scale, bias: [N] f32 (bias may be NULL); comp: [N]
+ * s32 as produced by gcb200_colsum_s8 (NULL = no compensation); out: [M,N] f32;
+ * acc_out: optional [M,N] s32 receiving the raw accumulators (bit-exact check).
+ */
+int gcb200_matmul_u8s8(const void *A, const void *W, const float *scale, const float *bias, const int32_t *comp,
+                       float *out, int32_t *acc_out, int64_t M, int64_t N, int64_t K, void *stream);
+int gcb200_colsum_s8(const void *W, int32_t *comp, int64_t K, int64_t N, int32_t zp_a, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Exact-order f32 matmul (+bias, ReLU) for f32 graphs — the form the reference's
+ * C-API test exercises (test/dnnl/TestApiOps.cpp:69-119).  CUDA cores, k
+ * ascending, separate multiply and add. */
+int gcb200_matmul_f32(const float *A, const float *B, const float *bias, float *Y, int64_t M, int64_t N, int64_t K,
+                      int transpose_a, int transpose_b, int relu, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Tile selection (the GPU counterpart of MatmulConfig, include/gc/Analysis/
+ * MatmulConfigAnalysis.h:25-34, chosen by MatmulConfigAnalysis.cpp:435-552).
+ * Pure host logic; needs no device. */
+typedef struct {
+  int swapped, bn, splits, stages, group_m, grid;
+} gcb200_matmul_config;
+int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count,
+                                gcb200_matmul_config *cfg);
+
+/* bf16 matmul with an explicit tile configuration (tuning, tests). */
+int gcb200_matmul_bf16_cfg(const void *A, const void *B, const void *bias, void *Y, int64_t M, int64_t N, int64_t K,
+                           int transpose_a, int transpose_b, int relu, const gcb200_matmul_config *cfg, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Microkernel runtime ABI of the reference
+ * (include/gc/ExecutionEngine/CPURuntime/Microkernel/BrgemmInterface.h:31-63):
+ * same names, argument meaning and units (elements); A, B, C are DEVICE
+ * pointers here.  dtype codes are dnnl_data_type_t (bf16 = 2, f32 = 3, s8 = 5,
+ * u8 = 6).  B is plain [K][LDB] for f32 and VNNI-packed for bf16
+ * ([K/2][LDB][2]) and int8 ([K/4][LDB][4]), as in BrgemmNaive.cpp:71-140.
+ * Calls are enqueued on the legacy default stream. */
+int64_t dnnl_brgemm_dispatch(int64_t M, int64_t N, int64_t K, int64_t LDA, int64_t LDB, int64_t LDC, int64_t stride_a,
+                             int64_t stride_b, float beta, int64_t dtypeA, int64_t dtypeB);
+void dnnl_brgemm_tileconfig(int64_t kernel);
+void dnnl_brgemm_tilerelease(void);
+void dnnl_brgemm_execute(int64_t kernel, void *A, uint64_t A_offset, void *B, uint64_t B_offset, void *C,
+                         uint64_t C_offset, int num);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GC_B200_H */
