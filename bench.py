@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 backend on the reference's headline partitions.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload mlp|gemm8192|...]
+
+Headline workload (``config.workload``): BASELINE configs[2], the bf16 MLP chain
+512 x (4096 -> 16384 -> 4096 -> 16384 -> 4096), bias + ReLU per layer, synthetic
+inputs with benchgc's fill semantics (N(0,1) input, N(0,0.02) weights, zero biases).
+One step = one pass of the whole partition.  Metric: TFLOPS (2*M*N*K per layer).
+
+  value     device-resident inputs, CUDA events on the launching stream, max over ranks
+  e2e       the same partition through dnnl_graph_compiler_execute with pinned HOST buffers:
+            per step H2D of the activations, D2H of the result (weights are constant
+            tensors: uploaded by the first call, resident afterwards)
+  roofline  tensor-bound: algorithmic FLOPs per GEMM launch / average launch time in the
+            timed region, against the measured cuBLAS bf16 peak of this pool
+  cpu_baseline  the reference's CPU path on a bounded sample (rank 0, N=1)
+
+Under torchrun (N>1) the layers are column/row tensor-parallel with one f32
+all-reduce (NCCL) per layer pair; total work is fixed, so scaling is "strong".
+``--impl reference`` times the reference's CPU implementation instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "graph-compiler_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+HIDDEN = (4096, 16384, 4096, 16384, 4096)
+BATCH = 512
+WORKLOAD = "mlp_bf16_b512_4096x16384x4096x16384x4096_bias_relu"
+
+
+def mlp_flops(batch=BATCH, hidden=HIDDEN):
+    return sum(2 * batch * hidden[i] * hidden[i + 1] for i in range(len(hidden) - 1))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(burst=d["bf16_tflops"], sustained=d["bf16_tflops_sustained"], hbm=d["hbm_gbs"], source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+# --------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.lines, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------- CPU baseline
+def cpu_reference_run(steps: int, warmup: int, rows: int | None = None):
+    """The reference's CPU implementation of the path on this host's cores, on a bounded sample:
+    `rows` rows of the 512-row batch through all four layers (rows of a batch are independent, so
+    work scales linearly).  Uses the reference's own naive brgemm (oracle/_ref, compiled unmodified)
+    driven by the restated deep-tile nest when present, else the oracle port."""
+    import numpy as np
+
+    import oracle
+
+    cores = len(os.sched_getaffinity(0))
+    oracle.set_num_threads(cores)
+    kind = "reference" if oracle.have_ref() else "port"
+    if rows is None:
+        rows = 32 if kind == "reference" else 128
+    rng = np.random.default_rng(0)
+    X = oracle.f32_to_bf16(rng.standard_normal((rows, HIDDEN[0])).astype(np.float32))
+    Ws = [oracle.f32_to_bf16((rng.standard_normal((HIDDEN[i], HIDDEN[i + 1])) * 0.02).astype(np.float32)) for i in range(4)]
+    Bs = [np.zeros(HIDDEN[i + 1], np.uint16) for i in range(4)]
+
+    def one():
+        h = X
+        for W, b in zip(Ws, Bs):
+            if kind == "reference":
+                h = oracle.linear_bf16_brgemm_nest(h, W, b, relu=True, backend="ref")
+            else:
+                h = oracle.linear_bf16(h, W, b, relu=True)
+        return h
+
+    for _ in range(warmup):
+        one()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    fl = mlp_flops(rows)
+    sample = (f"{rows} of {BATCH} batch rows through all 4 layers ({fl / 1e9:.2f} GFLOP per step); "
+              + ("reference BrgemmNaive.cpp (unmodified, oracle/_ref) driven by the restated deep-tile nest, OpenMP over output blocks"
+                 if kind == "reference" else "oracle port (vectorised restatement), OpenMP over rows"))
+    return dict(value=fl / dt / 1e12, unit="TFLOPS", cores=cores, kind=kind, sample=sample, ms_per_step=dt * 1e3)
+
+
+def cpu_onednn_class(rows=BATCH):
+    """Context only: torch CPU bf16 matmul (oneDNN brgemm, the kernel family BrgemmOnednn.cpp wraps)."""
+    import torch
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, HIDDEN[0]).bfloat16()
+    ws = [(torch.randn(HIDDEN[i], HIDDEN[i + 1]) * 0.02).bfloat16() for i in range(4)]
+    bs = [torch.zeros(HIDDEN[i + 1]).bfloat16() for i in range(4)]
+
+    def one():
+        h = x
+        for w, b in zip(ws, bs):
+            h = torch.relu(torch.mm(h, w) + b)
+        return h
+
+    one()
+    t0 = time.perf_counter()
+    n = 2
+    for _ in range(n):
+        one()
+    dt = (time.perf_counter() - t0) / n
+    return dict(value=mlp_flops(rows) / dt / 1e12, unit="TFLOPS", cores=torch.get_num_threads(),
+                what="torch.mm bf16 on CPU (oneDNN), full batch")
+
+
+# --------------------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="also time the other BASELINE configs (extra keys)")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    config = {"workload": WORKLOAD, "batch": BATCH, "hidden": list(HIDDEN), "fill": "src N(0,1), weights N(0,0.02), bias 0 (benchgc fill flags)",
+              "l2": "inputs larger than L2 (weights 512 MiB are re-read every step)"}
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        r = cpu_reference_run(max(1, min(a.steps, 3)), min(a.warmup, 1))
+        line = {"impl": "reference", "metric": "TFLOPS", "value": r["value"], "unit": "TFLOPS", "n_gpus": a.gpus,
+                "steps": max(1, min(a.steps, 3)), "warmup": min(a.warmup, 1), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": r["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from gc_b200 import api, lib, partitions
+    from gc_b200 import benchgc_compat as bc
+    from gc_b200.tensor_parallel import TensorParallelMLP, shard_weights
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- synthetic inputs (benchgc fills: seed + argument index)
+    X_host = bc.fill_tensor((BATCH, HIDDEN[0]), "bf16", "N", (0, 1), 0).pin_memory()
+    W_host = [bc.fill_tensor((HIDDEN[i], HIDDEN[i + 1]), "bf16", "N", (0, 0.02), 1 + i) for i in range(4)]
+    B_host = [torch.zeros(HIDDEN[i + 1], dtype=torch.bfloat16) for i in range(4)]
+    out_host = torch.empty(BATCH, HIDDEN[-1], dtype=torch.bfloat16).pin_memory()
+    flops = mlp_flops()
+
+    if world == 1:
+        js, in_ids, out_id = partitions.mlp(BATCH, HIDDEN, "bf16", [True] * 4, "relu", constant_weights=True)
+        exe = api.GraphCompiler().compile(js)
+        Xd = X_host.to(dev)
+        Wd = [w.to(dev) for w in W_host]
+        Bd = [b.to(dev) for b in B_host]
+        outd = torch.empty(BATCH, HIDDEN[-1], dtype=torch.bfloat16, device=dev)
+        dev_in, dev_out = dict(zip(in_ids, [Xd] + Wd + Bd)), {out_id: outd}
+
+        def step_device():
+            exe.execute_on_stream(dev_in, dev_out)
+
+        W_pin = [w.pin_memory() for w in W_host]
+        B_pin = [b.pin_memory() for b in B_host]
+        host_in, host_out = dict(zip(in_ids, [X_host] + W_pin + B_pin)), {out_id: out_host}
+
+        def step_e2e():
+            exe.execute(host_in, host_out)   # H2D of X, 4 launches, D2H of the result, synchronous
+
+        parallelism = "single GPU"
+    else:
+        ws, bs = shard_weights([w.to(dev) for w in W_host], [b.to(dev) for b in B_host], world, rank)
+        tp = TensorParallelMLP(ws, bs, relu=True)
+        Xd = X_host.to(dev)
+        holder = {}
+
+        def step_device():
+            holder["y"] = tp.step(Xd)
+
+        def step_e2e():
+            x = X_host.to(dev, non_blocking=True)
+            y = tp.step(x)
+            if rank == 0:
+                out_host.copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        parallelism = f"tp{world}: layers 1,3 column-parallel, layers 2,4 row-parallel + f32 all-reduce (NCCL)"
+    config["parallelism"] = parallelism
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, sample_clocks=False):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        if sampler:
+            sampler.start()
+        l0 = lib.launch_count()
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.record()
+        for _ in range(steps):
+            fn()
+        en.record()
+        barrier()
+        launches = lib.launch_count() - l0
+        ms = st.elapsed_time(en)
+        clocks = sampler.stop() if sampler else None
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps, launches, clocks
+
+    ms_dev, launches, clocks = timed(step_device, a.steps, a.warmup, sample_clocks=True)
+    ms_e2e, _, _ = timed(step_e2e, max(3, a.steps // 2), a.warmup)
+    assert lib.device_error() == 0, "a kernel reported a bounded-wait time-out"
+
+    peaks = measured_peaks()
+    gemm_launches = launches  # every launch in the timed region is one of this library's kernels
+    per_launch_ms = ms_dev * a.steps / max(launches, 1)
+    flops_per_launch = flops / (launches / a.steps) / world
+    achieved = flops_per_launch / per_launch_ms / 1e9
+    region_s = ms_dev * a.steps / 1e3
+    peak_kind = "sustained" if region_s >= 1.0 else "burst"
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get("gemm_kernel_mlp_layer_bytes_per_launch")
+
+    line = {
+        "metric": "TFLOPS", "value": flops / ms_dev / 1e9, "unit": "TFLOPS", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": config,
+        "e2e": {"value": flops / ms_e2e / 1e9, "unit": "TFLOPS", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": X_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                "note": "weights are property_type=constant: uploaded by the first (warm-up) call, resident afterwards"},
+        "gpu_launches": int(gemm_launches),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s", "frac": achieved / peaks[peak_kind],
+                     "traffic": traffic, "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind}",
+                     "kernel": "gemm_kernel<bf16, f32 accumulate> (tcgen05 + TMA), incl. launch gaps",
+                     "frac_of_vendor_dense_2250": achieved / 2250.0},
+    }
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        r = cpu_reference_run(1, 0)
+        line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        try:
+            line["cpu_onednn_class"] = cpu_onednn_class()
+        except Exception as e:  # context only
+            line["cpu_onednn_class"] = {"error": repr(e)[:100]}
+    if a.sweep and world == 1:
+        from gc_b200 import sweep
+
+        line["sweep"] = sweep.run_all(dev)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

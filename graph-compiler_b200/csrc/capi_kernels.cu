@@ -81,6 +81,12 @@ GCB_EXPORT int gcb200_device_error(void *stream, int *code) {
   });
 }
 
+GCB_EXPORT int gcb200_launch_count(uint64_t *count) {
+  if (!count) return GCB200_INVALID_ARGUMENT;
+  *count = launch_count();
+  return GCB200_OK;
+}
+
 GCB_EXPORT int gcb200_sm_count(int *count) {
   return guarded([&] {
     require(count != nullptr, "count is null");
@@ -264,6 +270,17 @@ GCB_EXPORT void dnnl_brgemm_execute(int64_t kernel, void *A, uint64_t A_offset, 
     else if (d.dtA == DT_U8 && d.dtB == DT_U8) launch_brgemm<uint8_t, uint8_t, int32_t, 4>(d, A, A_offset, B, B_offset, C, C_offset, num);
     else throw std::logic_error("dnnl_brgemm_execute: unsupported dtype pair");
     GCB_CUDA(cudaGetLastError());
+    count_launch();
   });
   (void)rc;
+}
+
+#include "attention.h"
+GCB_EXPORT int gcb200_attention_bf16(const void *Q, const void *K, const void *V, void *O, int64_t batch_heads,
+                                     int64_t seq, int64_t head_dim, float scale, int causal, void *stream) {
+  return guarded([&] {
+    require(Q && K && V && O && batch_heads > 0 && seq > 0 && head_dim > 0, "bad arguments");
+    device_state();
+    attention_bf16(Q, K, V, O, batch_heads, seq, head_dim, scale, causal, static_cast<cudaStream_t>(stream));
+  });
 }

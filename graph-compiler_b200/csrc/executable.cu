@@ -1,0 +1,543 @@
+// The oneDNN-graph backend C API (include/dnnl_graph_compiler.h) on top of the
+// CUDA runtime: compile = read the JSON partition + build the launch plan;
+// execute = marshal tensors by id, stage host buffers, run the plan's steps on
+// the executable's stream inside its pre-planned workspace arena.
+//
+// Reference counterparts: src/dnnl/dnnl_graph_compiler.cpp:45-226 (executable,
+// argument marshalling, status mapping) and lib/gc/ExecutionEngine/Driver/
+// Driver.cpp:60-89 (the JIT engine this replaces).
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include <cuda_fp16.h>
+
+#include "../../include/dnnl_graph_compiler.h"
+#include "../../include/gc_b200.h"
+#include "attention.h"
+#include "graph.h"
+#include "runtime.h"
+#include "sm100_ptx.cuh"
+
+#define GCB_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace gcb {
+
+extern thread_local std::string g_last_error;
+
+// ----------------------------------------------------------------------------- elementwise kernels
+constexpr int kMaxRank = 12; // DNNL_MAX_NDIMS
+
+struct EwParams {
+  int rank;
+  long long total;
+  long long dims[kMaxRank];   // output dims
+  long long sa[kMaxRank];     // element strides of operand a per output dim (0 = broadcast)
+  long long sb[kMaxRank];
+  int fn;                     // binary: 0 add 1 sub 2 mul 3 div; unary: 0 relu 1 sigmoid 2 pow 3 cast
+  float beta;
+  int dt_a, dt_b, dt_o;       // 0 f32, 1 bf16, 2 f16
+};
+
+__device__ __forceinline__ float ew_load(const void *p, long long i, int dt) {
+  if (dt == 0) return reinterpret_cast<const float *>(p)[i];
+  if (dt == 1) return bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p)[i]);
+  return __half2float(reinterpret_cast<const __half *>(p)[i]);
+}
+// Every bf16/f16 op rounds once on store: the reference evaluates low-precision
+// elementwise ops as extf -> f32 op -> truncf (lib/gc/Transforms/Pipeline.cpp:81-90).
+__device__ __forceinline__ void ew_store(void *p, long long i, int dt, float v) {
+  if (dt == 0) reinterpret_cast<float *>(p)[i] = v;
+  else if (dt == 1) reinterpret_cast<uint16_t *>(p)[i] = uint16_t(f32_to_bf16_bits(v));
+  else reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+}
+
+__global__ void binary_kernel(EwParams p, const void *a, const void *b, void *o) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
+    long long r = i, oa = 0, ob = 0;
+    for (int d = p.rank - 1; d >= 0; --d) {
+      const long long c = r % p.dims[d];
+      r /= p.dims[d];
+      oa += c * p.sa[d];
+      ob += c * p.sb[d];
+    }
+    const float x = ew_load(a, oa, p.dt_a), y = ew_load(b, ob, p.dt_b);
+    float v;
+    switch (p.fn) {
+    case 0: v = __fadd_rn(x, y); break;
+    case 1: v = __fsub_rn(x, y); break;
+    case 2: v = __fmul_rn(x, y); break;
+    default: v = __fdiv_rn(x, y); break;
+    }
+    ew_store(o, i, p.dt_o, v);
+  }
+}
+
+__global__ void unary_kernel(EwParams p, const void *a, void *o) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
+    long long r = i, oa = 0;
+    for (int d = p.rank - 1; d >= 0; --d) {
+      const long long c = r % p.dims[d];
+      r /= p.dims[d];
+      oa += c * p.sa[d];
+    }
+    const float x = ew_load(a, oa, p.dt_a);
+    float v;
+    switch (p.fn) {
+    case 0: v = (x != x) ? x : (x > 0.f ? x : 0.f); break;       // max(x, 0), NaN propagates
+    case 1: v = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-x))); break; // 1 / (1 + exp(-x))
+    case 2:
+      if (p.beta == 2.f) v = __fmul_rn(x, x);
+      else if (p.beta == 1.f) v = x;
+      else if (p.beta == 0.5f) v = sqrtf(x);
+      else if (p.beta == 3.f) v = __fmul_rn(__fmul_rn(x, x), x);
+      else v = powf(x, p.beta);
+      break;
+    default: v = x; break;
+    }
+    ew_store(o, i, p.dt_o, v);
+  }
+}
+
+struct ReduceParams {
+  int rank;
+  long long out_total, red_total;
+  long long kdims[kMaxRank], kstr[kMaxRank]; // kept dims (output iteration) and their input strides
+  int nk;
+  long long rdims[kMaxRank], rstr[kMaxRank]; // reduced dims, row-major order, input strides
+  int nr;
+  int mean;
+  int dt_a, dt_o;
+};
+
+// One thread per output element; the reduced indices are visited in ascending
+// row-major order, the order of the reference's linalg.reduce loops.
+__global__ void reduce_kernel(ReduceParams p, const void *a, void *o) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.out_total; i += (long long)gridDim.x * blockDim.x) {
+    long long r = i, base = 0;
+    for (int d = p.nk - 1; d >= 0; --d) {
+      base += (r % p.kdims[d]) * p.kstr[d];
+      r /= p.kdims[d];
+    }
+    float s = 0.f;
+    for (long long j = 0; j < p.red_total; ++j) {
+      long long q = j, off = base;
+      for (int d = p.nr - 1; d >= 0; --d) {
+        off += (q % p.rdims[d]) * p.rstr[d];
+        q /= p.rdims[d];
+      }
+      s = __fadd_rn(s, ew_load(a, off, p.dt_a));
+    }
+    if (p.mean) s = __fdiv_rn(s, float(p.red_total));
+    ew_store(o, i, p.dt_o, s);
+  }
+}
+
+static int ew_dtype(DType t) {
+  switch (t) {
+  case DType::F32: return 0;
+  case DType::BF16: return 1;
+  case DType::F16: return 2;
+  default: throw std::logic_error(std::string("elementwise op on dtype ") + dtype_name(t));
+  }
+}
+
+static std::vector<int64_t> dense_strides(const std::vector<int64_t> &shape) {
+  std::vector<int64_t> s(shape.size(), 1);
+  for (int d = int(shape.size()) - 2; d >= 0; --d) s[d] = s[d + 1] * shape[d + 1];
+  return s;
+}
+static std::vector<int64_t> strides_of(const LogicalTensor &t) {
+  if (t.strided && t.stride.size() == t.shape.size()) return t.stride;
+  return dense_strides(t.shape);
+}
+static bool is_dense(const LogicalTensor &t) { return strides_of(t) == dense_strides(t.shape); }
+// elements spanned in memory by a (possibly strided) tensor
+static size_t span_elems(const LogicalTensor &t) {
+  if (t.numel() == 0) return 0;
+  const auto s = strides_of(t);
+  int64_t span = 1;
+  for (size_t d = 0; d < t.shape.size(); ++d) span += (t.shape[d] - 1) * s[d];
+  return size_t(span);
+}
+
+// ----------------------------------------------------------------------------- executable
+struct DeviceBuffer {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  const void *cached_host = nullptr; // constant tensors: host address whose contents are resident
+  void reserve(size_t n) {
+    if (n <= bytes) return;
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    bytes = 0;
+    GCB_CUDA(cudaMalloc(&ptr, n));
+    bytes = n;
+  }
+  ~DeviceBuffer() {
+    if (ptr) cudaFree(ptr);
+  }
+};
+
+} // namespace gcb
+
+using namespace gcb;
+
+struct dnnl_graph_compiler {
+  uint32_t num_threads = 0;
+};
+
+struct dnnl_graph_compiler_executable {
+  Plan plan;
+  // device state is created on first execute so that compile needs no GPU
+  mutable std::mutex mu;
+  mutable bool ready = false;
+  mutable int device = -1;
+  mutable cudaStream_t stream = nullptr;
+  mutable DeviceBuffer arena;
+  mutable std::vector<DeviceBuffer> in_stage, out_stage;
+  mutable std::vector<char> comp_ready; // per QMATMUL scratch: column sums computed for a cached constant weight
+
+  explicit dnnl_graph_compiler_executable(const std::string &json) : plan(build_plan(read_partition(json))) {}
+  ~dnnl_graph_compiler_executable() {
+    if (stream) cudaStreamDestroy(stream);
+  }
+
+  void prepare() const {
+    if (ready) return;
+    DeviceState &d = device_state();
+    device = d.device;
+    GCB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    if (plan.arena_bytes) arena.reserve(plan.arena_bytes);
+    in_stage.resize(plan.part.input_ids.size());
+    out_stage.resize(plan.part.output_ids.size());
+    comp_ready.assign(plan.scratch.size(), 0);
+    ready = true;
+  }
+
+  static dnnl_graph_compiler_tensor *find(dnnl_graph_compiler_tensor *ts, size_t n, size_t i, size_t id) {
+    if (ts[i].id == id) return &ts[i];
+    for (size_t j = 0; j < n; ++j)   // the order may differ from the argument order
+      if (ts[j].id == id) return &ts[j];
+    throw std::invalid_argument("Tensor not found");
+  }
+
+  static bool on_device(const void *p) {
+    cudaPointerAttributes at;
+    cudaError_t e = cudaPointerGetAttributes(&at, p);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+  }
+
+  void check_dims(const dnnl_graph_compiler_tensor *t, const LogicalTensor &lt) const {
+    if (t->ndims > DNNL_MAX_NDIMS) throw std::invalid_argument("Number of dimensions > DNNL_MAX_NDIMS");
+    int64_t n = 1;
+    for (int d = 0; d < t->ndims; ++d) n *= t->dims[d];
+    if (n != lt.numel()) throw std::invalid_argument("Tensor " + std::to_string(lt.id) + " does not have the compiled shape");
+    if (!t->data && n) throw std::invalid_argument("Tensor " + std::to_string(lt.id) + " has no data");
+  }
+
+  // own_stream: run on the executable's private stream (the synchronous C API); otherwise on
+  // `user_stream`, where a null handle means the legacy default stream, as everywhere in CUDA.
+  void execute(dnnl_graph_compiler_tensor *inputs, dnnl_graph_compiler_tensor *outputs, cudaStream_t user_stream,
+               bool own_stream, bool sync) const {
+    std::lock_guard<std::mutex> g(mu);
+    prepare();
+    cudaStream_t s = own_stream ? stream : user_stream;
+    const Partition &p = plan.part;
+    const size_t ni = p.input_ids.size(), no = p.output_ids.size();
+    std::vector<void *> in_ptr(ni), out_ptr(no), out_host(no, nullptr);
+    for (size_t i = 0; i < ni; ++i) {
+      const LogicalTensor &lt = p.tensors.at(p.input_ids[i]);
+      dnnl_graph_compiler_tensor *t = find(inputs, ni, i, lt.id);
+      check_dims(t, lt);
+      const size_t bytes = span_elems(lt) * dtype_bytes(lt.dtype);
+      if (on_device(t->data)) {
+        in_ptr[i] = t->data;
+      } else {
+        DeviceBuffer &b = in_stage[i];
+        const bool resident = lt.constant && b.cached_host == t->data && b.bytes >= bytes;
+        if (!resident) {
+          b.reserve(bytes);
+          GCB_CUDA(cudaMemcpyAsync(b.ptr, t->data, bytes, cudaMemcpyHostToDevice, s));
+          b.cached_host = lt.constant ? t->data : nullptr;
+          for (size_t k = 0; k < comp_ready.size(); ++k) comp_ready[k] = 0;
+        }
+        in_ptr[i] = b.ptr;
+      }
+    }
+    for (size_t i = 0; i < no; ++i) {
+      const LogicalTensor &lt = p.tensors.at(p.output_ids[i]);
+      dnnl_graph_compiler_tensor *t = find(outputs, no, i, lt.id);
+      check_dims(t, lt);
+      const size_t bytes = size_t(lt.numel()) * dtype_bytes(lt.dtype);
+      if (on_device(t->data)) {
+        out_ptr[i] = t->data;
+      } else {
+        out_stage[i].reserve(bytes);
+        out_ptr[i] = out_stage[i].ptr;
+        out_host[i] = t->data;
+      }
+    }
+    auto addr = [&](size_t id) -> void * {
+      const TensorSlot &sl = plan.slots.at(id);
+      if (sl.where == TensorSlot::INPUT) return in_ptr[sl.index];
+      if (sl.where == TensorSlot::OUTPUT) return out_ptr[sl.index];
+      return static_cast<uint8_t *>(arena.ptr) + sl.offset;
+    };
+    for (const Step &st : plan.steps) run_step(st, addr, in_ptr, s);
+    for (size_t i = 0; i < no; ++i)
+      if (out_host[i]) {
+        const LogicalTensor &lt = p.tensors.at(p.output_ids[i]);
+        GCB_CUDA(cudaMemcpyAsync(out_host[i], out_ptr[i], size_t(lt.numel()) * dtype_bytes(lt.dtype), cudaMemcpyDeviceToHost, s));
+      }
+    bool any_host = false;
+    for (void *h : out_host) any_host |= (h != nullptr);
+    if (sync || any_host) {
+      GCB_CUDA(cudaStreamSynchronize(s));
+      int code = 0;
+      GCB_CUDA(cudaMemcpy(&code, device_state().d_error, sizeof(int), cudaMemcpyDeviceToHost));
+      if (code) {
+        GCB_CUDA(cudaMemset(device_state().d_error, 0, sizeof(int)));
+        throw std::runtime_error("a kernel gave up a bounded wait (code " + std::to_string(code) + ")");
+      }
+    }
+  }
+
+  template <class Addr>
+  void run_step(const Step &st, Addr &addr, const std::vector<void *> &in_ptr, cudaStream_t s) const {
+    const Partition &p = plan.part;
+    switch (st.kind) {
+    case StepKind::MATMUL: {
+      const LogicalTensor &A = p.tensors.at(st.in[0]);
+      if (!is_dense(A) || !is_dense(p.tensors.at(st.in[1]))) throw std::logic_error("MatMul operands must be dense row-major");
+      const void *bias = st.has_bias ? addr(st.in[2]) : nullptr;
+      if (A.dtype == DType::BF16) {
+        const void *a = addr(st.in[0]), *b = addr(st.in[1]);
+        if (tma_compatible(a, st.trans_a ? st.M : st.K, 2) && tma_compatible(b, st.trans_b ? st.K : st.N, 2)) {
+          MatmulArgs m;
+          m.A = a; m.B = b; m.M = st.M; m.N = st.N; m.K = st.K; m.trans_a = st.trans_a; m.trans_b = st.trans_b;
+          m.out_kind = OUT_BF16; m.out = addr(st.out[0]);
+          m.bias_kind = bias ? BIAS_BF16 : BIAS_NONE; m.bias = bias; m.relu = st.relu;
+          matmul_tc(m, s);
+        } else {
+          matmul_simt(a, b, bias, addr(st.out[0]), st.M, st.N, st.K, st.trans_a, st.trans_b, 1, st.relu, s);
+        }
+      } else {
+        matmul_simt(addr(st.in[0]), addr(st.in[1]), bias, addr(st.out[0]), st.M, st.N, st.K, st.trans_a, st.trans_b, 0,
+                    st.relu, s);
+      }
+      break;
+    }
+    case StepKind::QMATMUL: {
+      const TensorSlot &sc = plan.scratch[size_t(st.scratch_slot)];
+      int32_t *comp = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(arena.ptr) + sc.offset);
+      // the column sums depend on the weights only: recompute unless the weights are a cached constant
+      const TensorSlot &wslot = plan.slots.at(st.in[1]);
+      const bool w_const = wslot.where == TensorSlot::INPUT && p.tensors.at(st.in[1]).constant &&
+                           in_stage[wslot.index].cached_host != nullptr;
+      if (!(w_const && comp_ready[size_t(st.scratch_slot)])) {
+        colsum_s8(static_cast<const int8_t *>(addr(st.in[1])), comp, st.K, st.N, int32_t(st.zp_a), s);
+        comp_ready[size_t(st.scratch_slot)] = w_const ? 1 : 0;
+      }
+      MatmulArgs m;
+      m.A = addr(st.in[0]); m.B = addr(st.in[1]); m.M = st.M; m.N = st.N; m.K = st.K; m.int8 = 1;
+      m.out_kind = OUT_DEQUANT_F32; m.out = addr(st.out[0]);
+      m.scale = static_cast<const float *>(addr(st.in[2]));
+      m.comp = comp;
+      m.bias_kind = st.has_bias ? BIAS_F32 : BIAS_NONE;
+      m.bias = st.has_bias ? addr(st.in[3]) : nullptr;
+      m.acc_dump = st.out.size() > 1 ? static_cast<int32_t *>(addr(st.out[1])) : nullptr;
+      m.relu = st.relu;
+      if (!(tma_compatible(m.A, st.K, 1) && tma_compatible(m.B, st.N, 1)))
+        throw std::logic_error("QuantizedMatMul needs K and N to be multiples of 16");
+      matmul_tc(m, s);
+      break;
+    }
+    case StepKind::SDPA: {
+      attention_bf16(addr(st.in[0]), addr(st.in[1]), addr(st.in[2]), addr(st.out[0]), st.batch * st.heads, st.seq, st.dim,
+                     st.scale, st.causal ? 1 : 0, s);
+      break;
+    }
+    case StepKind::BINARY:
+    case StepKind::UNARY: {
+      const LogicalTensor &O = p.tensors.at(st.out[0]);
+      EwParams e{};
+      e.rank = int(O.shape.size());
+      if (e.rank > kMaxRank) throw std::invalid_argument("Number of dimensions > DNNL_MAX_NDIMS");
+      e.total = O.numel();
+      e.fn = st.fn;
+      e.beta = st.beta;
+      e.dt_o = ew_dtype(O.dtype);
+      for (int d = 0; d < e.rank; ++d) e.dims[d] = O.shape[size_t(d)];
+      auto fill = [&](const LogicalTensor &T, long long *dst) {
+        const auto str = strides_of(T);
+        const int off = e.rank - int(T.shape.size());
+        if (off < 0) throw std::invalid_argument("operand rank exceeds result rank");
+        for (int d = 0; d < e.rank; ++d) dst[d] = 0;
+        for (size_t d = 0; d < T.shape.size(); ++d) {
+          if (T.shape[d] == O.shape[d + off]) dst[d + off] = T.shape[d] == 1 ? 0 : str[d];
+          else if (T.shape[d] == 1) dst[d + off] = 0;
+          else throw std::invalid_argument("shapes are not broadcastable");
+        }
+      };
+      const LogicalTensor &A = p.tensors.at(st.in[0]);
+      fill(A, e.sa);
+      e.dt_a = ew_dtype(A.dtype);
+      const int threads = 256;
+      const int blocks = int(std::min<long long>((e.total + threads - 1) / threads, 148LL * 16));
+      if (e.total == 0) break;
+      if (st.kind == StepKind::BINARY) {
+        const LogicalTensor &B = p.tensors.at(st.in[1]);
+        fill(B, e.sb);
+        e.dt_b = ew_dtype(B.dtype);
+        binary_kernel<<<blocks, threads, 0, s>>>(e, addr(st.in[0]), addr(st.in[1]), addr(st.out[0]));
+      } else {
+        unary_kernel<<<blocks, threads, 0, s>>>(e, addr(st.in[0]), addr(st.out[0]));
+      }
+      GCB_CUDA(cudaGetLastError());
+      count_launch();
+      break;
+    }
+    case StepKind::REDUCE: {
+      const LogicalTensor &A = p.tensors.at(st.in[0]);
+      const LogicalTensor &O = p.tensors.at(st.out[0]);
+      ReduceParams r{};
+      const auto str = strides_of(A);
+      r.rank = int(A.shape.size());
+      if (r.rank > kMaxRank) throw std::invalid_argument("Number of dimensions > DNNL_MAX_NDIMS");
+      r.out_total = 1;
+      r.red_total = 1;
+      for (int d = 0; d < r.rank; ++d) {
+        const bool red = std::find(st.axes.begin(), st.axes.end(), int64_t(d)) != st.axes.end();
+        if (red) { r.rdims[r.nr] = A.shape[size_t(d)]; r.rstr[r.nr++] = str[size_t(d)]; r.red_total *= A.shape[size_t(d)]; }
+        else { r.kdims[r.nk] = A.shape[size_t(d)]; r.kstr[r.nk++] = str[size_t(d)]; r.out_total *= A.shape[size_t(d)]; }
+      }
+      if (r.out_total != O.numel()) throw std::invalid_argument("reduce output shape does not match");
+      r.mean = st.mean ? 1 : 0;
+      r.dt_a = ew_dtype(A.dtype);
+      r.dt_o = ew_dtype(O.dtype);
+      const int threads = 128;
+      const int blocks = int(std::min<long long>((r.out_total + threads - 1) / threads, 148LL * 16));
+      reduce_kernel<<<std::max(blocks, 1), threads, 0, s>>>(r, addr(st.in[0]), addr(st.out[0]));
+      GCB_CUDA(cudaGetLastError());
+      count_launch();
+      break;
+    }
+    default: throw std::logic_error("unsupported step");
+    }
+    (void)in_ptr;
+  }
+};
+
+// ----------------------------------------------------------------------------- C API
+#ifndef GCB_VERSION_MAJOR
+#define GCB_VERSION_MAJOR 0
+#define GCB_VERSION_MINOR 1
+#define GCB_VERSION_PATCH 0
+#endif
+
+GCB_EXPORT const dnnl_graph_compiler_version *dnnl_graph_compiler_get_version(void) {
+  static const dnnl_graph_compiler_version ver = {
+      {DNNL_GC_API_V_MAJOR, DNNL_GC_API_V_MINOR, DNNL_GC_API_V_PATCH, DNNL_GC_API_V_HASH},
+      {GCB_VERSION_MAJOR, GCB_VERSION_MINOR, GCB_VERSION_PATCH, "b200"}};
+  return &ver;
+}
+
+GCB_EXPORT dnnl_status_t dnnl_graph_compiler_create(const dnnl_graph_compiler_context *ctx, const dnnl_graph_compiler **gc) {
+  try {
+    auto *g = new dnnl_graph_compiler();
+    g->num_threads = ctx ? ctx->num_threads : 0;
+    *gc = g;
+    return dnnl_success;
+  } catch (const std::bad_alloc &) {
+    return dnnl_out_of_memory;
+  } catch (...) {
+    return dnnl_runtime_error;
+  }
+}
+
+GCB_EXPORT void dnnl_graph_compiler_destroy(const dnnl_graph_compiler *gc) { delete gc; }
+
+GCB_EXPORT dnnl_status_t dnnl_graph_compiler_compile(const dnnl_graph_compiler *gc, const char *graph_json,
+                                                     const dnnl_graph_compiler_executable **exe) {
+  (void)gc;
+  try {
+    if (!graph_json || !exe) throw std::invalid_argument("null argument");
+    *exe = new dnnl_graph_compiler_executable(std::string(graph_json));
+    return dnnl_success;
+  } catch (const std::invalid_argument &e) {
+    g_last_error = e.what();
+    return dnnl_invalid_graph;
+  } catch (const std::logic_error &e) {
+    g_last_error = e.what();
+    return dnnl_unimplemented;
+  } catch (const std::bad_alloc &) {
+    return dnnl_out_of_memory;
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+    return dnnl_runtime_error;
+  } catch (...) {
+    return dnnl_runtime_error;
+  }
+}
+
+GCB_EXPORT void dnnl_graph_compiler_destroy_executable(const dnnl_graph_compiler_executable *exe) { delete exe; }
+
+static dnnl_status_t execute_impl(const dnnl_graph_compiler_executable *exe, dnnl_graph_compiler_tensor *inputs,
+                                  dnnl_graph_compiler_tensor *outputs, cudaStream_t stream, bool own_stream, bool sync) {
+  try {
+    if (!exe) throw std::invalid_argument("null executable");
+    exe->execute(inputs, outputs, stream, own_stream, sync);
+    return dnnl_success;
+  } catch (const std::bad_alloc &) {
+    return dnnl_out_of_memory;
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+    return dnnl_runtime_error; // the reference maps every execute failure to runtime_error (:217-225)
+  } catch (...) {
+    return dnnl_runtime_error;
+  }
+}
+
+GCB_EXPORT dnnl_status_t dnnl_graph_compiler_execute(const dnnl_graph_compiler_executable *exe,
+                                                     dnnl_graph_compiler_tensor *inputs,
+                                                     dnnl_graph_compiler_tensor *outputs) {
+  return execute_impl(exe, inputs, outputs, nullptr, true, true);
+}
+
+// --- additions declared in include/gc_b200.h ---------------------------------------------------
+GCB_EXPORT int gcb200_execute_on_stream(const dnnl_graph_compiler_executable *exe, dnnl_graph_compiler_tensor *inputs,
+                                        dnnl_graph_compiler_tensor *outputs, void *stream) {
+  return int(execute_impl(exe, inputs, outputs, static_cast<cudaStream_t>(stream), false, false));
+}
+
+GCB_EXPORT int gcb200_plan_dump(const dnnl_graph_compiler_executable *exe, char *buf, size_t cap, size_t *needed) {
+  if (!exe) return GCB200_INVALID_ARGUMENT;
+  const std::string s = exe->plan.dump();
+  if (needed) *needed = s.size() + 1;
+  if (buf && cap) {
+    const size_t n = std::min(cap - 1, s.size());
+    std::memcpy(buf, s.data(), n);
+    buf[n] = '\0';
+  }
+  return GCB200_OK;
+}
+
+GCB_EXPORT int gcb200_plan_arena(const int64_t *bytes, const int *first, const int *last, int n, int64_t align,
+                                 int64_t *offsets, int64_t *total) {
+  if (n < 0 || align <= 0 || !offsets || !total) return GCB200_INVALID_ARGUMENT;
+  std::vector<BufferLife> b;
+  for (int i = 0; i < n; ++i) b.push_back(BufferLife{size_t(bytes[i]), first[i], last[i]});
+  std::vector<size_t> off;
+  *total = int64_t(plan_arena(b, size_t(align), off));
+  for (int i = 0; i < n; ++i) offsets[i] = int64_t(off[size_t(i)]);
+  return GCB200_OK;
+}

@@ -4,6 +4,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -13,6 +14,10 @@
 namespace gcb {
 
 // ----------------------------------------------------------------------------- device state
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
 static std::mutex g_dev_mutex;
 static DeviceState g_devs[64];
 
@@ -128,7 +133,7 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
       const int t = ceil_div(M, 128) * ceil_div(N, bn_eff);
       const int waves = ceil_div(t, sm_count);
       const double useful = double(M) * double(N) / (double(waves) * sm_count * 128.0 * bn_eff);
-      const double reuse = bn_eff >= 256 ? 1.0 : (bn_eff >= 128 ? 0.88 : 0.70);
+      const double reuse = bn_eff >= 256 ? 1.0 : (bn_eff >= 128 ? 0.72 : 0.50); // measured: 804 / 582 TFLOPS at 4096^3
       const double score = useful * reuse;
       if (score > best + 1e-9) { best = score; best_bn = bn_eff; }
     }
@@ -304,6 +309,7 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   else         e = cfg.swapped ? launch_gemm_kernel<1, true>(tmA, tmB, p, grid, smem, stream)
                                : launch_gemm_kernel<1, false>(tmA, tmB, p, grid, smem, stream);
   if (e != cudaSuccess) throw CudaError(std::string("gemm launch: ") + cudaGetErrorString(e));
+  count_launch();
   if (split) {
     if (ld_out != a.N) throw std::invalid_argument("split-K with a strided output is not supported");
     reduce_planes(planes, cfg.splits, a.M * a.N, a.out, a.M, a.N, a.out_kind, a.bias_kind, a.bias, a.scale, a.comp,
@@ -370,6 +376,7 @@ void reduce_planes(const void *parts, int nparts, int64_t plane, void *out, int6
     reduce_planes_kernel<false><<<blocks, threads, 0, stream>>>(parts, nparts, plane, out, M, N, out_kind, bias_kind,
                                                                bias, scale, comp, acc_dump, relu);
   GCB_CUDA(cudaGetLastError());
+  count_launch();
 }
 
 void reduce_epilogue_bf16(const float *parts, int nparts, int64_t plane, const void *bias_bf16, void *out_bf16,
@@ -393,6 +400,7 @@ void colsum_s8(const int8_t *W, int32_t *comp, int64_t K, int64_t N, int32_t zp,
   dim3 grid(unsigned((N + 255) / 256), unsigned(std::min<int64_t>(K, 64)));
   colsum_s8_kernel<<<grid, 256, 0, stream>>>(W, comp, K, N, zp);
   GCB_CUDA(cudaGetLastError());
+  count_launch();
 }
 
 // Exact-order SIMT matmul: every output element accumulates k ascending with a
@@ -469,6 +477,7 @@ void matmul_simt(const void *A, const void *B, const void *bias, void *out, int6
   else
     matmul_simt_kernel<1><<<grid, 256, 0, stream>>>(A, B, bias, out, int(M), int(N), int(K), trans_a, trans_b, relu);
   GCB_CUDA(cudaGetLastError());
+  count_launch();
 }
 
 } // namespace gcb

@@ -99,4 +99,8 @@ void matmul_simt(const void *A, const void *B, const void *bias, void *out, int6
 
 int read_device_error(cudaStream_t stream); // synchronises the stream; returns and clears the error word
 
+// Kernel launches issued by this library since load (every launcher counts its own).
+void count_launch(int n = 1);
+unsigned long long launch_count();
+
 } // namespace gcb

@@ -1,0 +1,181 @@
+"""Python mirror of the oneDNN-graph backend C API (``include/dnnl_graph_compiler.h``).
+
+``GraphCompiler.compile(json)`` -> ``Executable``; ``Executable.execute(inputs, outputs)``
+takes ``{tensor id: array}`` dictionaries, the way the reference's C API matches
+tensors by id (src/dnnl/dnnl_graph_compiler.cpp:64-103).  Arrays may be numpy
+arrays / CPU torch tensors (host pointers; staged by the library) or CUDA torch
+tensors (device pointers; used in place).  The 3-method surface
+(compile / execute / destroy) follows python/gc_mlir/graph_compiler.py:17-45 of
+the reference (compile, jit, compile_and_jit) collapsed onto the C API.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict
+
+from . import lib as _lib
+
+# dnnl_status_t
+SUCCESS, OUT_OF_MEMORY, INVALID_ARGUMENTS, UNIMPLEMENTED = 0, 1, 2, 3
+RUNTIME_ERROR, INVALID_GRAPH = 5, 7
+
+_STATUS = {0: "success", 1: "out_of_memory", 2: "invalid_arguments", 3: "unimplemented", 5: "runtime_error",
+           7: "invalid_graph"}
+
+
+class DnnlError(RuntimeError):
+    def __init__(self, status: int, msg: str = ""):
+        super().__init__(f"dnnl status {status} ({_STATUS.get(status, '?')}) {msg}")
+        self.status = status
+
+
+class Context(C.Structure):
+    _fields_ = [("num_threads", C.c_uint32)]
+
+
+class Tensor(C.Structure):
+    _fields_ = [("id", C.c_size_t), ("ndims", C.c_uint8), ("dims", C.POINTER(C.c_int64)), ("data", C.c_void_p)]
+
+
+class _VersionPart(C.Structure):
+    _fields_ = [("major", C.c_uint8), ("minor", C.c_uint8), ("patch", C.c_uint8), ("hash", C.c_char_p)]
+
+
+class Version(C.Structure):
+    _fields_ = [("api_version", _VersionPart), ("gc_version", _VersionPart)]
+
+
+def _bind():
+    l = _lib.load()
+    if getattr(l, "_gc_api_bound", False):
+        return l
+    l.dnnl_graph_compiler_get_version.restype = C.POINTER(Version)
+    l.dnnl_graph_compiler_create.argtypes = [C.POINTER(Context), C.POINTER(C.c_void_p)]
+    l.dnnl_graph_compiler_create.restype = C.c_int
+    l.dnnl_graph_compiler_destroy.argtypes = [C.c_void_p]
+    l.dnnl_graph_compiler_destroy.restype = None
+    l.dnnl_graph_compiler_compile.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]
+    l.dnnl_graph_compiler_compile.restype = C.c_int
+    l.dnnl_graph_compiler_destroy_executable.argtypes = [C.c_void_p]
+    l.dnnl_graph_compiler_destroy_executable.restype = None
+    l.dnnl_graph_compiler_execute.argtypes = [C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor)]
+    l.dnnl_graph_compiler_execute.restype = C.c_int
+    l.gcb200_execute_on_stream.argtypes = [C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]
+    l.gcb200_execute_on_stream.restype = C.c_int
+    l.gcb200_plan_dump.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
+    l.gcb200_plan_dump.restype = C.c_int
+    l.gcb200_plan_arena.argtypes = [C.POINTER(C.c_int64), C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.c_int64,
+                                    C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+    l.gcb200_plan_arena.restype = C.c_int
+    l._gc_api_bound = True
+    return l
+
+
+def get_version():
+    v = _bind().dnnl_graph_compiler_get_version().contents
+    return ((v.api_version.major, v.api_version.minor, v.api_version.patch, v.api_version.hash.decode()),
+            (v.gc_version.major, v.gc_version.minor, v.gc_version.patch, v.gc_version.hash.decode()))
+
+
+def _describe(a):
+    """-> (data pointer, shape) of a numpy array or torch tensor."""
+    if hasattr(a, "data_ptr"):
+        return a.data_ptr(), tuple(a.shape)
+    return a.ctypes.data, tuple(a.shape)
+
+
+def _pack(tensors: Dict[int, object], order=None):
+    ids = list(tensors.keys()) if order is None else list(order)
+    arr = (Tensor * max(len(ids), 1))()
+    keep = []
+    for i, tid in enumerate(ids):
+        ptr, shape = _describe(tensors[tid])
+        dims = (C.c_int64 * max(len(shape), 1))(*shape)
+        keep.append(dims)
+        arr[i] = Tensor(tid, len(shape), dims, ptr)
+    return arr, keep
+
+
+class Executable:
+    def __init__(self, handle):
+        self._h = handle
+
+    def execute(self, inputs: Dict[int, object], outputs: Dict[int, object]) -> None:
+        """Synchronous, like the reference: results are in ``outputs`` on return."""
+        i_arr, k1 = _pack(inputs)
+        o_arr, k2 = _pack(outputs)
+        st = _bind().dnnl_graph_compiler_execute(self._h, i_arr, o_arr)
+        if st != SUCCESS:
+            raise DnnlError(st, _lib.load().gcb200_last_error().decode(errors="replace"))
+
+    def execute_on_stream(self, inputs, outputs, stream=None) -> None:
+        """Device tensors only: enqueue on ``stream`` (default: torch's current) and return."""
+        import torch
+
+        s = C.c_void_p((stream or torch.cuda.current_stream()).cuda_stream)
+        i_arr, k1 = _pack(inputs)
+        o_arr, k2 = _pack(outputs)
+        st = _bind().gcb200_execute_on_stream(self._h, i_arr, o_arr, s)
+        if st != SUCCESS:
+            raise DnnlError(st, _lib.load().gcb200_last_error().decode(errors="replace"))
+
+    def plan(self) -> str:
+        n = C.c_size_t(0)
+        _bind().gcb200_plan_dump(self._h, None, 0, C.byref(n))
+        buf = C.create_string_buffer(n.value)
+        _bind().gcb200_plan_dump(self._h, buf, n.value, None)
+        return buf.value.decode()
+
+    def destroy(self):
+        if self._h:
+            _bind().dnnl_graph_compiler_destroy_executable(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class GraphCompiler:
+    def __init__(self, num_threads: int | None = None):
+        l = _bind()
+        h = C.c_void_p()
+        ctx = Context(num_threads) if num_threads is not None else None
+        st = l.dnnl_graph_compiler_create(C.byref(ctx) if ctx is not None else None, C.byref(h))
+        if st != SUCCESS:
+            raise DnnlError(st)
+        self._h = h
+
+    def compile(self, graph_json: str) -> Executable:
+        h = C.c_void_p()
+        st = _bind().dnnl_graph_compiler_compile(self._h, graph_json.encode(), C.byref(h))
+        if st != SUCCESS:
+            raise DnnlError(st, _lib.load().gcb200_last_error().decode(errors="replace"))
+        return Executable(h)
+
+    def destroy(self):
+        if self._h:
+            _bind().dnnl_graph_compiler_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def plan_arena(sizes, first, last, align=64):
+    """Offsets and total size for buffers live over step ranges [first, last]."""
+    n = len(sizes)
+    b = (C.c_int64 * n)(*sizes)
+    f = (C.c_int * n)(*first)
+    la = (C.c_int * n)(*last)
+    off = (C.c_int64 * n)()
+    tot = C.c_int64(0)
+    st = _bind().gcb200_plan_arena(b, f, la, n, align, off, C.byref(tot))
+    if st != 0:
+        raise ValueError("bad arena request")
+    return list(off), tot.value

@@ -46,6 +46,8 @@ def load() -> C.CDLL:
     sig = {
         "gcb200_device_error": [_vp, C.POINTER(_int)],
         "gcb200_sm_count": [C.POINTER(_int)],
+        "gcb200_launch_count": [C.POINTER(_u64)],
+        "gcb200_attention_bf16": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp],
         "gcb200_matmul_bf16": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
         "gcb200_matmul_bf16_cfg": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig), _vp],
         "gcb200_matmul_bf16_f32out": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
@@ -88,6 +90,12 @@ def _stream():
 def sm_count() -> int:
     n = _int(0)
     check(load().gcb200_sm_count(C.byref(n)))
+    return n.value
+
+
+def launch_count() -> int:
+    n = _u64(0)
+    check(load().gcb200_launch_count(C.byref(n)))
     return n.value
 
 
@@ -176,4 +184,17 @@ def matmul_f32(A, B, bias=None, relu=False, transpose_a=False, transpose_b=False
     out = torch.empty((M, N), dtype=torch.float32, device=A.device)
     check(load().gcb200_matmul_f32(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), M, N, K, int(transpose_a), int(transpose_b),
                                    int(relu), _stream()))
+    return out
+
+
+def attention_bf16(Q, K, V, scale: float, causal: bool = False, out=None):
+    """Fused attention on bf16 CUDA tensors [..., S, D] (leading dims are independent units)."""
+    import torch
+
+    assert Q.is_contiguous() and K.is_contiguous() and V.is_contiguous() and Q.dtype == torch.bfloat16
+    S, D = Q.shape[-2:]
+    bh = Q.numel() // (S * D)
+    if out is None:
+        out = torch.empty_like(Q)
+    check(load().gcb200_attention_bf16(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), bh, S, D, float(scale), int(causal), _stream()))
     return out

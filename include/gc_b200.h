@@ -42,6 +42,10 @@ const char *gcb200_last_error(void);
  * the bounded wait that gave up).  Synchronises `stream`. */
 int gcb200_device_error(void *stream, int *code);
 
+/* Kernel launches this library has issued since it was loaded (all launchers,
+ * all threads).  Benchmarks difference it around a timed region. */
+int gcb200_launch_count(uint64_t *count);
+
 /* Number of SMs of the current device (persistent grids are sized from it). */
 int gcb200_sm_count(int *count);
 
@@ -109,6 +113,35 @@ int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes
 /* bf16 matmul with an explicit tile configuration (tuning, tests). */
 int gcb200_matmul_bf16_cfg(const void *A, const void *B, const void *bias, void *Y, int64_t M, int64_t N, int64_t K,
                            int transpose_a, int transpose_b, int relu, const gcb200_matmul_config *cfg, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Fused attention (extension: the reference has softmax and matmul pieces but no
+ * fused pattern — lib/gc/Transforms/DecomposeAggregatedOps.cpp:24-38 defines the
+ * softmax it would use).  O = softmax(Q K^T * scale [+ causal mask]) V, softmax
+ * in f32; Q, K, V, O: [batch*heads][seq][head_dim] bf16, contiguous. */
+int gcb200_attention_bf16(const void *Q, const void *K, const void *V, void *O, int64_t batch_heads, int64_t seq,
+                          int64_t head_dim, float scale, int causal, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Additions around the dnnl_graph_compiler_* API (declared in
+ * dnnl_graph_compiler.h; tensor struct repeated here as an opaque pointer to
+ * keep this header standalone).
+ *
+ * gcb200_execute_on_stream: like dnnl_graph_compiler_execute
+ * (src/dnnl/dnnl_graph_compiler.cpp:214-226) but enqueues on the caller's stream
+ * and returns without synchronising when every tensor is a device pointer.
+ * gcb200_plan_dump: text form of the compiled launch plan (steps, fused post-ops,
+ * arena offsets) — the counterpart of the reference's --ir_printing
+ * (python/gc_mlir/graph_compiler.py:30-34).  Needs no device.
+ * gcb200_plan_arena: the workspace planner by itself (role of
+ * lib/gc/Transforms/StaticMemoryPlanning.cpp:628-652). */
+struct dnnl_graph_compiler_executable;
+struct dnnl_graph_compiler_tensor;
+int gcb200_execute_on_stream(const struct dnnl_graph_compiler_executable *exe, struct dnnl_graph_compiler_tensor *inputs,
+                             struct dnnl_graph_compiler_tensor *outputs, void *stream);
+int gcb200_plan_dump(const struct dnnl_graph_compiler_executable *exe, char *buf, size_t cap, size_t *needed);
+int gcb200_plan_arena(const int64_t *bytes, const int *first, const int *last, int n, int64_t align, int64_t *offsets,
+                      int64_t *total);
 
 /* ---------------------------------------------------------------------------
  * Microkernel runtime ABI of the reference

@@ -1,0 +1,204 @@
+"""Host-side tests of the C ABI: the library loads and exports what the headers
+declare, the JSON reader accepts/rejects what the reference's reader does
+(status classes of src/dnnl/dnnl_graph_compiler.cpp:193-206), the launch plan
+fuses post-ops, the arena planner never overlaps live buffers.  No GPU needed —
+compile is host-only, like the reference's."""
+import ctypes as C
+import json
+import os
+import re
+
+import pytest
+
+from gc_b200 import api, lib, partitions
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_JSON = "/root/reference/test/dnnl/resources"
+
+
+def test_library_exports_every_declared_symbol():
+    l = lib.load()
+    declared = set()
+    for h in ("gc_b200.h", "dnnl_graph_compiler.h"):
+        src = open(os.path.join(ROOT, "include", h)).read()
+        src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+        declared |= set(re.findall(r"\b((?:gcb200|dnnl_graph_compiler|dnnl_brgemm)_\w+)\s*\(", src))
+    assert len(declared) >= 20
+    for name in sorted(declared):
+        assert hasattr(l, name), f"{name} is declared but not exported"
+
+
+def test_version():
+    apiv, gcv = api.get_version()
+    assert apiv[:3] == (0, 1, 0)
+    assert all(x != 255 for x in gcv[:3])  # test/dnnl/TestApiBasic.cpp:69-72
+
+
+def test_create_accepts_null_context_and_compile_is_host_only():
+    gc = api.GraphCompiler()          # ctx == NULL, as test/dnnl/TestApiOps.cpp:45
+    gc4 = api.GraphCompiler(num_threads=4)
+    js, ins, out = partitions.mlp(128, (512, 256))
+    exe = gc.compile(js)
+    assert "MatMul+ReLU" in exe.plan()
+    exe.destroy(); gc.destroy(); gc4.destroy()
+
+
+def _status(js):
+    gc = api.GraphCompiler()
+    try:
+        gc.compile(js).destroy()
+        return api.SUCCESS
+    except api.DnnlError as e:
+        return e.status
+    finally:
+        gc.destroy()
+
+
+def _base():
+    return json.loads(partitions.mlp(8, (16, 8))[0])
+
+
+def test_error_classes_follow_the_reference_reader():
+    assert _status(json.dumps(_base())) == api.SUCCESS
+    g = _base(); g["bogus"] = 1
+    assert _status(json.dumps(g)) == api.INVALID_GRAPH            # unrecognised key (JsonParser.cpp:70)
+    g = _base(); g["graph"][0]["kind"] = "Convolution"
+    assert _status(json.dumps(g)) == api.UNIMPLEMENTED            # unsupported op (JsonParser.cpp:155)
+    g = _base(); g["engine_kind"] = "fpga"
+    assert _status(json.dumps(g)) == api.UNIMPLEMENTED            # :49
+    g = _base(); g["fpmath_mode"] = "bf16"
+    assert _status(json.dumps(g)) == api.UNIMPLEMENTED            # :54-57
+    g = _base(); g["graph"][0]["inputs"][0]["dtype"] = "f128"
+    assert _status(json.dumps(g)) == api.UNIMPLEMENTED            # :281
+    g = _base(); g["graph"][0]["inputs"][0]["layout_type"] = "opaque"
+    assert _status(json.dumps(g)) == api.UNIMPLEMENTED            # :293
+    g = _base(); g["graph"][0]["inputs"][0]["colour"] = "red"
+    assert _status(json.dumps(g)) == api.INVALID_GRAPH            # :301
+    g = _base(); del g["graph"][0]["kind"]
+    assert _status(json.dumps(g)) == api.INVALID_GRAPH            # :211
+    g = _base(); g["input_ports"] = g["input_ports"][:-1]
+    assert _status(json.dumps(g)) == api.INVALID_GRAPH            # :76-80
+    g = _base(); g["output_ports"] = [777]
+    assert _status(json.dumps(g)) == api.INVALID_GRAPH            # :100-104
+    g = _base(); g["graph"][0]["attrs"] = {"transpose_a": {"value": 1, "type": "bool"}}
+    assert _status(json.dumps(g)) == api.INVALID_GRAPH            # attr keys are ordered: type, value (:228-233)
+    g = _base(); g["graph"][0]["attrs"] = {"transpose_a": {"type": "complex", "value": 1}}
+    assert _status(json.dumps(g)) == api.UNIMPLEMENTED            # :256
+    g = _base(); g["graph"][1]["inputs"][0]["shape"] = [3, 3]
+    assert _status(json.dumps(g)) == api.INVALID_GRAPH            # type mismatch for a produced value (:196-199)
+    assert _status("{ not json") == api.INVALID_GRAPH
+    assert _status("[]") == api.INVALID_GRAPH
+
+
+def test_mpl_graph_structure():
+    """The 2-layer MLP of test/dnnl/resources/mpl.json (TestJsonParser.cpp:138-225): arguments
+    0,1,2,5,7 in first-use order, result 9; both spellings of bias (+ReLU) fuse into the matmuls."""
+    t = lambda i, s: {"id": i, "dtype": "bf16", "shape": s}
+    graph = [
+        {"kind": "MatMul", "inputs": [t(0, [128, 512]), t(1, [512, 64]), t(2, [64])], "outputs": [t(3, [128, 64])]},
+        {"kind": "ReLU", "inputs": [t(3, [128, 64])], "outputs": [t(4, [128, 64])]},
+        {"kind": "MatMul", "inputs": [t(4, [128, 64]), t(5, [64, 256])], "outputs": [t(6, [128, 256])]},
+        {"kind": "Add", "inputs": [t(6, [128, 256]), t(7, [256])], "outputs": [t(8, [128, 256])]},
+        {"kind": "ReLU", "inputs": [t(8, [128, 256])], "outputs": [t(9, [128, 256])]},
+    ]
+    js = json.dumps({"version": "3.5.0", "engine_kind": "cpu", "fpmath_mode": "any", "input_ports": [0, 1, 2, 5, 7],
+                     "output_ports": [9], "graph": graph})
+    gc = api.GraphCompiler()
+    plan = gc.compile(js).plan()
+    assert "inputs: 0 1 2 5 7" in plan and "outputs: 9" in plan
+    steps = [l for l in plan.splitlines() if l.startswith("step")]
+    assert len(steps) == 2
+    assert "MatMul+ReLU" in steps[0] and "bias=1 relu=1" in steps[0] and "4@arena+0" in steps[0]
+    assert "MatMul+Add+ReLU" in steps[1] and "bias=1 relu=1" in steps[1] and "9@out0" in steps[1]
+    assert "arena_bytes: 16384" in plan  # one 128x64 bf16 temporary
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_JSON), reason="reference fixtures not present")
+def test_reference_json_fixtures_compile():
+    """Every partition file the reference's C-API tests use compiles (test/dnnl/resources/*.json)."""
+    gc = api.GraphCompiler()
+    names = sorted(f for f in os.listdir(REF_JSON) if f.endswith(".json"))
+    assert len(names) == 13
+    for n in names:
+        exe = gc.compile(open(os.path.join(REF_JSON, n)).read())
+        assert exe.plan().count("step") >= 1, n
+
+
+def test_fusion_is_blocked_by_a_second_consumer_or_an_output():
+    t = lambda i, s: {"id": i, "dtype": "bf16", "shape": s}
+    graph = [
+        {"kind": "MatMul", "inputs": [t(0, [32, 64]), t(1, [64, 48])], "outputs": [t(2, [32, 48])]},
+        {"kind": "ReLU", "inputs": [t(2, [32, 48])], "outputs": [t(3, [32, 48])]},
+    ]
+    env = {"version": "3.5.0", "engine_kind": "cpu", "fpmath_mode": "strict", "graph": graph}
+    gc = api.GraphCompiler()
+    assert gc.compile(json.dumps(env)).plan().count("step") == 1
+    env["output_ports"] = [2, 3]            # the un-activated value is also a result
+    assert gc.compile(json.dumps(env)).plan().count("step") == 2
+    del env["output_ports"]
+    graph.append({"kind": "Add", "inputs": [t(2, [32, 48]), t(3, [32, 48])], "outputs": [t(4, [32, 48])]})
+    assert gc.compile(json.dumps(env)).plan().count("step") == 3
+
+
+def test_mlp_chain_ping_pongs_in_the_arena():
+    js, ins, out = partitions.mlp(512, (4096, 16384, 4096, 16384, 4096), has_bias=[True] * 4)
+    plan = api.GraphCompiler().compile(js).plan()
+    steps = [l for l in plan.splitlines() if l.startswith("step")]
+    assert len(steps) == 4 and all("MatMul+ReLU" in s for s in steps)
+    # live at once: one 512x16384 and one 512x4096 bf16 activation
+    assert "arena_bytes: %d" % (512 * 16384 * 2 + 512 * 4096 * 2) in plan
+
+
+def test_arena_planner_never_overlaps_live_buffers():
+    import random
+
+    rng = random.Random(0)
+    for trial in range(50):
+        n = rng.randint(1, 24)
+        sizes = [rng.choice([0, 1, 64, 100, 160, 4096, 5000]) for _ in range(n)]
+        first = [rng.randint(0, 20) for _ in range(n)]
+        last = [f + rng.randint(0, 6) for f in first]
+        off, total = api.plan_arena(sizes, first, last, align=64)
+        for i in range(n):
+            assert off[i] % 64 == 0 and off[i] + sizes[i] <= total
+            for j in range(i):
+                if first[i] <= last[j] and first[j] <= last[i] and sizes[i] and sizes[j]:
+                    assert off[i] + sizes[i] <= off[j] or off[j] + sizes[j] <= off[i], (trial, i, j)
+        peak = max(sum(s for s, f, l in zip(sizes, first, last) if f <= t <= l) for t in range(30))
+        assert total >= peak
+    # disjoint lifetimes share memory
+    off, total = api.plan_arena([1000, 1000, 1000], [0, 1, 2], [0, 1, 2], align=64)
+    assert total == 1024 and off == [0, 0, 0]
+
+
+def test_tile_selection_for_the_benchmark_shapes():
+    sel = lambda M, N, K, db=2, ob=2: lib.select_matmul_config(M, N, K, db, ob, 148)
+    c = sel(8192, 8192, 8192)
+    assert (c.swapped, c.bn, c.splits) == (0, 256, 1) and c.grid == 148
+    c = sel(16, 28672, 8192)            # decode shape: weights on the MMA M side, split-K to fill the SMs
+    assert c.swapped == 1 and c.bn == 16 and c.splits > 1
+    c = sel(128, 256, 512)              # BASELINE configs[0]
+    assert c.swapped == 0 and c.bn in (64, 128, 256)
+    c = sel(1024, 4096, 4096, 1, 4)     # int8
+    assert c.swapped == 0 and c.bn % 32 == 0
+    for M, N, K in [(1, 1, 1), (5, 7, 9), (200, 328, 136), (64, 128, 64), (65, 100000, 64)]:
+        c = sel(M, N, K)
+        assert 16 <= c.bn <= 256 and c.bn % 16 == 0 and 2 <= c.stages <= 8 and c.splits >= 1 and c.grid >= 1
+
+
+def test_launchers_fail_loudly_without_a_device():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    n = C.c_int(0)
+    assert lib.load().gcb200_sm_count(C.byref(n)) == 3  # GCB200_NO_DEVICE: no CPU fallback
+    assert b"CUDA" in lib.load().gcb200_last_error() or b"device" in lib.load().gcb200_last_error()
+    import numpy as np
+
+    js, ins, out = partitions.mlp(8, (16, 8), dtype="f32")
+    exe = api.GraphCompiler().compile(js)
+    with pytest.raises(api.DnnlError) as ei:
+        exe.execute({0: np.zeros((8, 16), np.float32), 1: np.zeros((16, 8), np.float32), 2: np.zeros(8, np.float32)},
+                    {out: np.zeros((8, 8), np.float32)})
+    assert ei.value.status == api.RUNTIME_ERROR
