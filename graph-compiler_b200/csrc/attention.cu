@@ -157,6 +157,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc_qk = umma_instr_desc(1, 1, 1, 0, 0, 128, 128);   // A, B K-major
+      // A (P) and B (V) must have the same 16-bit format: kind::f16 with an f16 A and a bf16 B operand
+      // raises an illegal-instruction fault on sm_100a, so P is rounded to bf16 like V
       const uint32_t idesc_pv = umma_instr_desc(1, 1, 1, 0, 1, 128, 128);   // B (V) MN-major
       const int nt[2] = {n0, n1};
       int err = 0;
@@ -285,7 +287,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             p1 = (c * 32 + i + 1 < lim) ? p1 : 0.f;
           }
           sum += p0 + p1;
-          pk[i >> 1] = f32_to_bf16_bits(p0) | (f32_to_bf16_bits(p1) << 16);
+pk[i >> 1] = f32_to_bf16_bits(p0) | (f32_to_bf16_bits(p1) << 16);
         }
         // 32 columns = 64 bytes = four 16-byte chunks of block (c >> 1), chunk index (c & 1) * 4 + k
         uint8_t *blk = pbuf + (c >> 1) * 16384 + row * 128;

@@ -142,15 +142,15 @@ GCB_EXPORT int gcb200_reduce_bias_act_bf16(const float *parts, int nparts, int64
 
 GCB_EXPORT int gcb200_matmul_u8s8(const void *A, const void *W, const float *scale, const float *bias,
                                   const int32_t *comp, float *out, int32_t *acc_out, int64_t M, int64_t N, int64_t K,
-                                  void *stream) {
+                                  int transpose_b, void *stream) {
   return guarded([&] {
     require(A && W && (out || acc_out), "null tensor pointer");
     require(!out || scale, "dequantised output needs scales");
     require(M > 0 && N > 0 && K > 0, "matmul dimensions must be positive");
-    if (!(tma_compatible(A, K, 1) && tma_compatible(W, N, 1)))
+    if (!(tma_compatible(A, K, 1) && tma_compatible(W, transpose_b ? K : N, 1)))
       throw std::logic_error("int8 matmul needs K and N to be multiples of 16 and 16-byte aligned bases");
     MatmulArgs a;
-    a.A = A; a.B = W; a.M = M; a.N = N; a.K = K; a.int8 = 1;
+    a.A = A; a.B = W; a.M = M; a.N = N; a.K = K; a.int8 = 1; a.trans_b = transpose_b;
     if (out) {
       a.out_kind = OUT_DEQUANT_F32; a.out = out; a.scale = scale; a.comp = comp;
       a.bias_kind = bias ? BIAS_F32 : BIAS_NONE; a.bias = bias; a.acc_dump = acc_out;

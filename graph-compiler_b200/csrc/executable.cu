@@ -286,6 +286,15 @@ struct dnnl_graph_compiler_executable {
         out_host[i] = t->data;
       }
     }
+    // The synchronous API runs on the executable's private stream.  Device tensors may still be
+    // being produced (or their memory still be in use) by work the caller queued on other streams;
+    // order this call after all of it.
+    if (own_stream) {
+      bool any_dev = false;
+      for (size_t i = 0; i < ni; ++i) any_dev |= (in_ptr[i] != in_stage[i].ptr);
+      for (size_t i = 0; i < no; ++i) any_dev |= (out_host[i] == nullptr);
+      if (any_dev) GCB_CUDA(cudaDeviceSynchronize());
+    }
     auto addr = [&](size_t id) -> void * {
       const TensorSlot &sl = plan.slots.at(id);
       if (sl.where == TensorSlot::INPUT) return in_ptr[sl.index];

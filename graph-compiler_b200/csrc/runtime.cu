@@ -186,7 +186,7 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
 }
 
 // ----------------------------------------------------------------------------- matmul planning
-static OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes) {
+OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes) {
   OperandGeom g{};
   const uint32_t bk = 128 / elem_bytes;  // K elements per stage
   g.mn_major = mn_major ? 1u : 0u;
@@ -210,7 +210,7 @@ static OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes) {
   return g;
 }
 
-static CUtensorMap operand_tmap(const OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
+CUtensorMap operand_tmap(const OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
                                 int64_t k_total, int tile_mn) {
   const uint32_t bk = 128 / elem_bytes;
   if (!g.mn_major)  // memory [mn_total][k_total], K contiguous

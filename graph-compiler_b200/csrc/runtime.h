@@ -61,6 +61,12 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
 // Whether the TMA path can take this operand layout (16-byte aligned base and row pitch).
 bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes);
 
+// Shared-memory stage geometry and tensor map of one GEMM operand tile (`tile_mn` rows of the MMA
+// M or N side; K contiguous in memory unless mn_major).
+OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes);
+CUtensorMap operand_tmap(const OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
+                         int64_t k_total, int tile_mn);
+
 // --------------------------------------------------------------------------- launchers
 struct MatmulArgs {
   const void *A = nullptr;      // [M,K] row-major, or [K,M] when trans_a

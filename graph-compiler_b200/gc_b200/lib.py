@@ -52,7 +52,7 @@ def load() -> C.CDLL:
         "gcb200_matmul_bf16_cfg": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig), _vp],
         "gcb200_matmul_bf16_f32out": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
         "gcb200_reduce_bias_act_bf16": [_vp, _int, _i64, _vp, _vp, _i64, _i64, _int, _vp],
-        "gcb200_matmul_u8s8": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
+        "gcb200_matmul_u8s8": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp],
         "gcb200_colsum_s8": [_vp, _vp, _i64, _i64, _i32, _vp],
         "gcb200_matmul_f32": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
         "gcb200_select_matmul_config": [_i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig)],
@@ -163,16 +163,16 @@ def colsum_s8(W, zp_a: int):
     return comp
 
 
-def matmul_u8s8(A, W, scale=None, bias=None, comp=None, want_acc=False):
-    """Returns (out f32 or None, acc s32 or None)."""
+def matmul_u8s8(A, W, scale=None, bias=None, comp=None, want_acc=False, transpose_b=False):
+    """Returns (out f32 or None, acc s32 or None).  W is [K,N], or [N,K] when transpose_b."""
     import torch
 
     M, K = A.shape
-    N = W.shape[1]
+    N = W.shape[0] if transpose_b else W.shape[1]
     out = torch.empty((M, N), dtype=torch.float32, device=A.device) if scale is not None else None
     acc = torch.empty((M, N), dtype=torch.int32, device=A.device) if (want_acc or out is None) else None
     check(load().gcb200_matmul_u8s8(_ptr(A), _ptr(W), _ptr(scale), _ptr(bias), _ptr(comp), _ptr(out), _ptr(acc), M, N, K,
-                                    _stream()))
+                                    int(transpose_b), _stream()))
     return out, acc
 
 

@@ -22,8 +22,9 @@
  * GcDnnlApi target; no call site changes.
  *
  * Differences in behaviour, all additive:
- *   - tensor `data` may be a HOST pointer (as in the reference; staged through
- *     pinned memory) or a DEVICE pointer (used in place, zero copy);
+ *   - tensor `data` may be a HOST pointer (as in the reference; copied to and from
+ *     the device by the call) or a DEVICE pointer (used in place, zero copy; the
+ *     call first waits for all work previously queued on the device, on any stream);
  *   - the JSON may carry the extension op kinds documented in INTEGRATION.md
  *     (int8 matmul with per-channel dequantisation, fused attention), which the
  *     reference's front end cannot express;

@@ -85,12 +85,13 @@ int gcb200_reduce_bias_act_bf16(const float *parts, int nparts, int64_t plane_st
  *
  *   acc = A_u8 . W_s8  (exact s32);  comp[n] = zp_a * sum_k W[k,n]
  *   out = float(acc - comp[n]) * scale[n] + bias[n]
- * A: [M,K] u8; W: [K,N] s8; scale, bias: [N] f32 (bias may be NULL); comp: [N]
+ * A: [M,K] u8; W: [K,N] s8 (or [N,K] when transpose_b: the K-contiguous form the
+ * tensor core reads fastest for 8-bit operands); scale, bias: [N] f32 (bias may be NULL); comp: [N]
  * s32 as produced by gcb200_colsum_s8 (NULL = no compensation); out: [M,N] f32;
  * acc_out: optional [M,N] s32 receiving the raw accumulators (bit-exact check).
  */
 int gcb200_matmul_u8s8(const void *A, const void *W, const float *scale, const float *bias, const int32_t *comp,
-                       float *out, int32_t *acc_out, int64_t M, int64_t N, int64_t K, void *stream);
+                       float *out, int32_t *acc_out, int64_t M, int64_t N, int64_t K, int transpose_b, void *stream);
 int gcb200_colsum_s8(const void *W, int32_t *comp, int64_t K, int64_t N, int32_t zp_a, void *stream);
 
 /* ---------------------------------------------------------------------------

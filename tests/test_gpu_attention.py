@@ -1,0 +1,69 @@
+"""Fused attention against the CPU oracle (f32 softmax restated from the reference's softmax
+decomposition; the reference has no fused pattern, so parity here is against the restatement)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from _util import bf16_f32, tbits
+from gc_b200 import api, lib, partitions
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(O, Q, K, V, scale, causal, what):
+    """|diff| <= 1e-2 |want| + 2^-8 * sum_j P_ij |V_jd|.
+
+    The tensor core needs both operands of P.V in one 16-bit format, so P is rounded to bf16 (unit
+    roundoff 2^-9) before the product: the result carries an error of up to 2^-9 * sum_j P_ij |V_jd|,
+    which is small against the row's terms but not against an output element that is a cancelled
+    sum.  The bound term is computed by the oracle itself (attention on |V|); twice the roundoff is
+    allowed, on top of the 1e-2 relative tolerance."""
+    want_bits = oracle.attention_bf16(tbits(Q), tbits(K), tbits(V), scale, causal)
+    mag_bits = oracle.attention_bf16(tbits(Q), tbits(K), tbits(V) & np.uint16(0x7FFF), scale, causal)
+    g, w = bf16_f32(tbits(O)).astype(np.float64), bf16_f32(want_bits).astype(np.float64)
+    mag = bf16_f32(mag_bits).astype(np.float64)
+    diff = np.abs(g - w)
+    tol = 1e-2 * np.abs(w) + 2.0 ** -8 * mag
+    bad = diff > tol
+    if bad.any():
+        idx = np.argwhere(bad)[:8]
+        detail = "; ".join(f"{tuple(int(x) for x in i)}: got {g[tuple(i)]:.6g} want {w[tuple(i)]:.6g}" for i in idx)
+        raise AssertionError(f"{what}: {int(bad.sum())} of {bad.size} outside tolerance; max_abs={diff.max():.4g}; {detail}")
+    return float(diff.max())
+
+
+@pytest.mark.parametrize("bh,S,causal", [(2, 256, False), (2, 256, True), (3, 128, False), (3, 128, True), (2, 384, True),
+                                          (2, 200, False), (2, 200, True), (1, 1000, True), (4, 512, False), (1, 64, True)])
+def test_attention_small(bh, S, causal):
+    D = 128
+    g = torch.Generator().manual_seed(S + bh)
+    Q, K, V = (torch.randn(bh, S, D, generator=g).bfloat16() for _ in range(3))
+    scale = 1.0 / math.sqrt(D)
+    O = lib.attention_bf16(Q.cuda(), K.cuda(), V.cuda(), scale, causal)
+    torch.cuda.synchronize()
+    assert lib.device_error() == 0
+    mx = _check(O, Q, K, V, scale, causal, f"bh={bh} S={S} causal={causal}")
+    print(f"attention bh={bh} S={S} causal={causal}: max_abs={mx:.4g}")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_full_size_units(causal):
+    """BASELINE configs[3]: batch 16, 32 heads, seq 2048, head_dim 128 through the SDPA partition;
+    (batch, head) units are independent, so the oracle recomputes a subset of them."""
+    B, H, S, D = 16, 32, 2048, 128
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Q, K, V = (torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16() for _ in range(3))
+    O = torch.empty_like(Q)
+    js, ins, out_id = partitions.sdpa(B, H, S, D, 1.0 / math.sqrt(D), causal)
+    exe = api.GraphCompiler().compile(js)
+    exe.execute({0: Q, 1: K, 2: V}, {out_id: O})
+    for b, h in [(0, 0), (7, 13), (15, 31)]:
+        mx = _check(O[b, h], Q[b, h], K[b, h], V[b, h], 1.0 / math.sqrt(D), causal, f"unit ({b},{h}) causal={causal}")
+    print(f"attention 16x32x2048x128 causal={causal}: max_abs={mx:.4g}")
+    # softmax rows sum to one: with V = 1 every output element is exactly 1 (up to bf16 rounding of P)
+    ones = torch.ones_like(V)
+    exe.execute({0: Q, 1: K, 2: ones}, {out_id: O})
+    assert float((O.float() - 1).abs().max()) < 2e-2

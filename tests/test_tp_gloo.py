@@ -1,0 +1,107 @@
+"""Host logic of the tensor-parallel MLP under gloo, world_size 2 and 4, on CPU.
+
+The compute calls are replaced by the CPU oracle (test infrastructure), so what is tested is the
+sharding, the order of collective and epilogue, and the numerics rule "f32 partial sums, reduce,
+then cast / bias / ReLU": the result must equal the oracle's single-device chain within the
+partial-sum reordering (bit-identical where sums are exact)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from gc_b200.tensor_parallel import TensorParallelMLP, shard_range, shard_weights
+
+
+def _bits(t):
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def _from_bits(a):
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+
+
+class OracleOps:
+    def linear(self, x, w, b, relu):
+        return _from_bits(oracle.linear_bf16(_bits(x), _bits(w), None if b is None else _bits(b), relu=relu))
+
+    def linear_partial(self, x, w):
+        _, acc = oracle.linear_bf16(_bits(x), _bits(w), return_acc=True)
+        return torch.from_numpy(acc)
+
+    def epilogue(self, partial, b, relu):
+        return _from_bits(oracle.reduce_epilogue_bf16(partial.numpy()[None], None if b is None else _bits(b), relu=relu))
+
+
+def _make(exact: bool):
+    g = torch.Generator().manual_seed(0)
+    hidden = (64, 256, 96, 128, 32)
+    if exact:   # small integers: every partial sum is exact, so any reduction order gives the same bits
+        X = torch.randint(-2, 3, (24, hidden[0]), generator=g).bfloat16()
+        Ws = [torch.randint(-1, 2, (hidden[i], hidden[i + 1]), generator=g).bfloat16() for i in range(4)]
+        Bs = [torch.randint(-2, 3, (hidden[i + 1],), generator=g).bfloat16() for i in range(4)]
+    else:
+        X = torch.randn(24, hidden[0], generator=g).bfloat16()
+        Ws = [(torch.randn(hidden[i], hidden[i + 1], generator=g) * 0.1).bfloat16() for i in range(4)]
+        Bs = [(torch.randn(hidden[i + 1], generator=g) * 0.1).bfloat16() for i in range(4)]
+    return X, Ws, Bs
+
+
+def _worker(rank, world, port, exact, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        X, Ws, Bs = _make(exact)
+        ws, bs = shard_weights(Ws, Bs, world, rank)
+        tp = TensorParallelMLP(ws, bs, relu=True, ops=OracleOps())
+        y = tp.step(X)
+        q.put((rank, _bits(y).copy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("exact", [True, False])
+def test_tensor_parallel_mlp_matches_single_device_chain(world, exact):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, exact, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = dict(q.get(timeout=180) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    X, Ws, Bs = _make(exact)
+    want = oracle.mlp_bf16(_bits(X), [_bits(w) for w in Ws], [_bits(b) for b in Bs], relu=True)
+    for r in range(world):
+        assert np.array_equal(outs[r], outs[0])          # every rank holds the full result
+    if exact:
+        assert np.array_equal(outs[0], want)
+    else:
+        g = (outs[0].astype(np.uint32) << 16).view(np.float32)
+        w = (want.astype(np.uint32) << 16).view(np.float32)
+        assert np.all(np.abs(g - w) <= 2e-2 * np.maximum(np.abs(w), np.sqrt(np.mean(w ** 2))))
+        assert (outs[0] == want).mean() > 0.9
+
+
+def test_shard_helpers():
+    assert shard_range(16384, 8, 3) == (6144, 8192)
+    with pytest.raises(ValueError):
+        shard_range(10, 4, 0)
+    W = [torch.zeros(8, 12), torch.zeros(12, 8)]
+    ws, bs = shard_weights(W, [torch.zeros(12), torch.zeros(8)], 4, 1)
+    assert ws[0].shape == (8, 3) and ws[1].shape == (3, 8) and bs[0].shape == (3,) and bs[1].shape == (8,)
+    with pytest.raises(ValueError):
+        TensorParallelMLP([W[0]], [None])
