@@ -47,6 +47,8 @@ def load() -> C.CDLL:
         "gcb200_device_error": [_vp, C.POINTER(_int)],
         "gcb200_sm_count": [C.POINTER(_int)],
         "gcb200_launch_count": [C.POINTER(_u64)],
+        "gcb200_matmul_bf16_splitk_static": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
+        "gcb200_static_error": [_vp, C.POINTER(_int)],
         "gcb200_attention_bf16": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp],
         "gcb200_matmul_bf16": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
         "gcb200_matmul_bf16_cfg": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig), _vp],

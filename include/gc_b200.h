@@ -145,6 +145,32 @@ int gcb200_plan_arena(const int64_t *bytes, const int *first, const int *last, i
                       int64_t *total);
 
 /* ---------------------------------------------------------------------------
+ * Split-K bf16 matmul that allocates nothing.  No counterpart in the reference
+ * (its runtime allocates freely from FILO pools); added for hosts that cannot
+ * let a library call cudaMalloc once they are running — a server that has given
+ * all device memory to its own pool, a latency-critical thread that must not
+ * take the driver's allocation lock, a runtime with a fixed memory budget.
+ *
+ *   Y = act( bf16( bf16(A . B) + bias ) ),  A [M,K], B [K,N], bias [N] or NULL, Y [M,N], bf16
+ *
+ * The f32 partial-sum planes (splits * M * N * 4 bytes) live in a 16 MiB array
+ * that is part of the loaded module: every GPU that loads the library holds it
+ * until exit.  Larger requests fail with GCB200_INVALID_ARGUMENT and a message
+ * naming both sizes.  `splits` <= 0 lets the library choose (at least 2).
+ * The array is shared by all calls and keeps the previous call's contents;
+ * nothing in it needs clearing, since each split writes its plane in full before
+ * the reduction reads it.  Calls that overlap on the GPU race on it: serialise
+ * calls per device.  The first call on a device resolves the array's device
+ * address and sets the kernel's shared-memory limit; issue it before starting
+ * any stream capture.  Neither this function nor gcb200_static_error calls
+ * cudaMalloc, cudaFree or any allocating routine.
+ * gcb200_static_error reads (and clears when non-zero) the module-resident word
+ * in which these kernels record a bounded wait that gave up. */
+int gcb200_matmul_bf16_splitk_static(const void *A, const void *B, const void *bias, void *Y, int64_t M, int64_t N,
+                                     int64_t K, int splits, int relu, void *stream);
+int gcb200_static_error(void *stream, int *code);
+
+/* ---------------------------------------------------------------------------
  * Microkernel runtime ABI of the reference
  * (include/gc/ExecutionEngine/CPURuntime/Microkernel/BrgemmInterface.h:31-63):
  * same names, argument meaning and units (elements); A, B, C are DEVICE
