@@ -169,6 +169,104 @@ def cpu_onednn_class(rows=BATCH):
                 what="torch.mm bf16 on CPU (oneDNN), full batch")
 
 
+# --------------------------------------------------------------------------------------- other BASELINE configs
+def run_case(spec: str, steps: int = 20, warmup: int = 5):
+    """Time one kernel-level case with device-resident inputs (CUDA events on the launching stream).
+
+    spec: gemm:M:N:K | decode | int8:M:N:K | attention:B:H:S:D:causal(0|1) | cfg1
+    Returns a dict with ms, value/unit, the roofline bound and fraction against the measured peak."""
+    import math
+
+    import torch
+
+    from gc_b200 import lib
+
+    peaks = measured_peaks()
+    f = spec.split(":")
+    kind = f[0]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def u(shape):
+        return (torch.rand(shape, generator=g, device=dev) * 2 - 1).bfloat16()
+
+    if kind in ("gemm", "decode", "cfg1"):
+        M, N, K = (16, 28672, 8192) if kind == "decode" else (128, 256, 512) if kind == "cfg1" else map(int, f[1:4])
+        A, B = u((M, K)), u((K, N))
+        bias = u((N,)) if kind == "cfg1" else None
+        Y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        fn = lambda: lib.matmul_bf16(A, B, bias, relu=(kind == "cfg1"), out=Y)
+        work, unit = 2.0 * M * N * K, "TFLOPS"
+        bytes_ = (M * K + K * N + M * N) * 2
+        l2_flush = bytes_ < 256e6
+    elif kind == "int8":
+        M, N, K = map(int, f[1:4])
+        A = torch.randint(0, 256, (M, K), generator=g, device=dev, dtype=torch.uint8)
+        W = torch.randint(-127, 128, (K, N), generator=g, device=dev, dtype=torch.int8)
+        sc = torch.rand(N, generator=g, device=dev) * 0.009 + 0.001
+        bi = torch.rand(N, generator=g, device=dev) * 2 - 1
+        comp = lib.colsum_s8(W, 128)
+        out = torch.empty(M, N, device=dev)
+        import ctypes as C
+        l = lib.load()
+        fn = lambda: lib.check(l.gcb200_matmul_u8s8(A.data_ptr(), W.data_ptr(), sc.data_ptr(), bi.data_ptr(), comp.data_ptr(),
+                                                    out.data_ptr(), None, M, N, K, 0, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        work, unit = 2.0 * M * N * K, "TOPS"
+        bytes_ = M * K + K * N + M * N * 4
+        l2_flush = True
+    elif kind == "attention":
+        B_, H, S, D, causal = map(int, f[1:6])
+        Q, Kt, V = (torch.randn(B_, H, S, D, generator=g, device=dev).bfloat16() for _ in range(3))
+        O = torch.empty_like(Q)
+        fn = lambda: lib.attention_bf16(Q, Kt, V, 1.0 / math.sqrt(D), bool(causal), out=O)
+        work, unit = 4.0 * B_ * H * S * S * D * (0.5 if causal else 1.0), "TFLOPS"
+        bytes_ = 4 * B_ * H * S * D * 2
+        l2_flush = bytes_ < 256e6
+    else:
+        raise ValueError(spec)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if l2_flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    l0 = lib.launch_count()
+    if flush is None:
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.record()
+        for _ in range(steps):
+            fn()
+        en.record()
+        torch.cuda.synchronize()
+        ms = st.elapsed_time(en) / steps
+    else:   # small working set: write a buffer larger than L2 between timed launches
+        tot = 0.0
+        for _ in range(steps):
+            flush.zero_()
+            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            st.record()
+            fn()
+            en.record()
+            torch.cuda.synchronize()
+            tot += st.elapsed_time(en)
+        ms = tot / steps
+    launches = (lib.launch_count() - l0) // steps
+    r = {"case": spec, "ms": ms, "value": work / ms / 1e9, "unit": unit, "launches_per_step": int(launches),
+         "l2": "flushed between launches" if flush is not None else "working set larger than L2"}
+    if kind == "decode":
+        r["roofline"] = {"bound": "hbm", "achieved": bytes_ / ms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": bytes_ / ms / 1e6 / peaks["hbm"]}
+    elif kind == "int8":
+        r["roofline"] = {"bound": "tensor", "achieved": work / ms / 1e9, "peak": 4500.0, "unit": "TOP/s", "frac": work / ms / 1e9 / 4500.0,
+                         "peak_source": "vendor dense int8 (no measured int8 figure on this pool)"}
+    else:
+        r["roofline"] = {"bound": "tensor", "achieved": work / ms / 1e9, "peak": peaks["burst"], "unit": "TFLOP/s",
+                         "frac": work / ms / 1e9 / peaks["burst"], "frac_of_vendor_dense_2250": work / ms / 1e9 / 2250.0}
+    return r
+
+
+SWEEP = ["cfg1", "int8:1024:4096:4096", "attention:16:32:2048:128:0", "attention:16:32:2048:128:1", "gemm:1024:1024:1024",
+         "gemm:2048:2048:2048", "gemm:4096:4096:4096", "gemm:8192:8192:8192", "gemm:16384:16384:16384", "decode"]
+
+
 # --------------------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -177,7 +275,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--sweep", action="store_true", help="also time the other BASELINE configs (extra keys)")
+    ap.add_argument("--sweep", action="store_true", help="also time the other BASELINE configs (extra key 'sweep')")
+    ap.add_argument("--case", default=None, help="time ONE kernel-level case instead (see run_case) and print its line; "
+                                                  "used for ncu captures of a single kernel")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
 
@@ -199,6 +299,13 @@ def main():
                 "e2e": {"value": r["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         print(json.dumps(line))
+        return
+
+    if a.case:
+        import torch
+
+        torch.cuda.set_device(local_rank)
+        print(json.dumps(run_case(a.case, a.steps, a.warmup)))
         return
 
     import torch
@@ -326,9 +433,7 @@ def main():
         except Exception as e:  # context only
             line["cpu_onednn_class"] = {"error": repr(e)[:100]}
     if a.sweep and world == 1:
-        from gc_b200 import sweep
-
-        line["sweep"] = sweep.run_all(dev)
+        line["sweep"] = [run_case(c, 10 if "16384" in c else 20, 3) for c in SWEEP]
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

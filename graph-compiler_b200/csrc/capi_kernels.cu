@@ -108,9 +108,10 @@ GCB_EXPORT int gcb200_matmul_bf16_cfg(const void *A, const void *B, const void *
     require(cfg != nullptr, "cfg is null");
     require(cfg->bn >= 16 && cfg->bn <= 256 && cfg->bn % 16 == 0, "bn must be a multiple of 16 in [16,256]");
     require(cfg->swapped || cfg->bn % 64 == 0, "bf16 output tiles need bn % 64 == 0");
+    require(!cfg->pair || (!cfg->swapped && cfg->bn % 128 == 0), "the CTA-pair kernel needs bn in {128, 256} and the row-major orientation");
     require(cfg->stages >= 2 && cfg->stages <= 8, "stages must be in [2,8]");
     require(cfg->splits >= 1 && cfg->group_m >= 1, "splits and group_m must be positive");
-    MatmulConfig c{cfg->swapped, cfg->bn, cfg->splits, cfg->stages, cfg->group_m, cfg->grid};
+    MatmulConfig c{cfg->swapped, cfg->bn, cfg->splits, cfg->stages, cfg->group_m, cfg->grid, cfg->pair};
     const int kb = int((K + 63) / 64);
     const int per = (kb + c.splits - 1) / c.splits;
     c.splits = (kb + per - 1) / per;
@@ -183,7 +184,7 @@ GCB_EXPORT int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int 
     require(cfg && M > 0 && N > 0 && K > 0 && sm_count > 0, "bad arguments");
     require(dtype_bytes == 1 || dtype_bytes == 2, "dtype_bytes must be 1 or 2");
     MatmulConfig c = select_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count);
-    *cfg = gcb200_matmul_config{c.swapped, c.bn, c.splits, c.stages, c.group_m, c.grid};
+    *cfg = gcb200_matmul_config{c.swapped, c.bn, c.splits, c.stages, c.group_m, c.grid, c.pair};
   });
 }
 

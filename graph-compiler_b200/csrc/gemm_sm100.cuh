@@ -27,6 +27,8 @@ struct OperandGeom {
   uint32_t lbo, sbo;   // descriptor leading / stride byte offsets
   uint32_t kstep;      // bytes to advance the start address per MMA K step
   uint32_t bytes;      // bytes per stage
+  uint32_t one_load;   // 1: the whole stage arrives with ONE TMA instruction (K-major: a 2-D box;
+                       //    MN-major: a 3-D box over [64-wide MN group][K][group index])
 };
 
 struct GemmParams {
@@ -65,5 +67,12 @@ cudaError_t launch_gemm_kernel(const CUtensorMap &tmA, const CUtensorMap &tmB, c
                                size_t smem, cudaStream_t stream);
 
 size_t gemm_smem_bytes(const GemmParams &p);
+
+// CTA-pair form (tcgen05 cta_group::2): 256 x BN tiles, p.tiles_m counts 256-row tiles, p.b is one
+// CTA's half of the B tile.  KIND as above; row-major output orientation only.
+template <int KIND>
+cudaError_t launch_gemm_pair_kernel(const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p, int grid,
+                                    size_t smem, cudaStream_t stream);
+size_t gemm_pair_smem_bytes(const GemmParams &p);
 
 } // namespace gcb

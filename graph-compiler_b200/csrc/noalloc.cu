@@ -112,6 +112,7 @@ GCB_EXPORT int gcb200_matmul_bf16_splitk_static(const void *A, const void *B, co
     StaticState &st = static_state();
 
     MatmulConfig cfg = select_matmul_config(M, N, K, 2, 4, st.sm_count);
+    cfg.pair = 0;   // this entry point drives the one-CTA kernel
     const int k_blocks = int((K + 63) / 64);
     int want = splits > 0 ? splits : std::max(2, cfg.splits);
     want = std::max(1, std::min(want, k_blocks));

@@ -103,6 +103,21 @@ CUtensorMap make_tmap_2d(ElemType t, const void *ptr, uint64_t inner, uint64_t o
   return m;
 }
 
+CUtensorMap make_tmap_3d(ElemType t, const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                         uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2) {
+  CUtensorMap m;
+  CUtensorMapDataType dt = (t == ElemType::BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode_fn()(&m, dt, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw CudaError("cuTensorMapEncodeTiled (3-D) failed with CUresult " + std::to_string(int(r)));
+  return m;
+}
+
 bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes) {
   return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && ((row_elems * elem_bytes) & 15) == 0;
 }
@@ -172,8 +187,9 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
   c.grid = std::min(tiles * c.splits, sm_count);
   if (const char *ov = std::getenv("GC_B200_TILE")) {
     // "bn,splits,stages,group_m" — any field may be 0 to keep the heuristic's choice
-    int bn = 0, sp = 0, st = 0, gm = 0;
-    if (std::sscanf(ov, "%d,%d,%d,%d", &bn, &sp, &st, &gm) >= 1) {
+    int bn = 0, sp = 0, st = 0, gm = 0, pr = -1;
+    if (std::sscanf(ov, "%d,%d,%d,%d,%d", &bn, &sp, &st, &gm, &pr) >= 1) {
+      if (pr >= 0) c.pair = pr;
       if (bn > 0 && !c.swapped) c.bn = bn;
       if (sp > 0) { const int per = ceil_div(k_blocks, sp); c.splits = ceil_div(k_blocks, per); }
       if (st > 0) c.stages = std::min(st, c.stages);
@@ -198,6 +214,7 @@ OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes) {
     g.sbo = 1024;
     g.kstep = 32;
     g.bytes = g.box_bytes;
+    g.one_load = 1;
   } else {
     g.box_mn = 128 / elem_bytes;
     g.boxes = (uint32_t(tile_mn) + g.box_mn - 1) / g.box_mn;
@@ -210,9 +227,19 @@ OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes) {
   return g;
 }
 
-CUtensorMap operand_tmap(const OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
+CUtensorMap operand_tmap(OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
                                 int64_t k_total, int tile_mn) {
   const uint32_t bk = 128 / elem_bytes;
+  if (g.mn_major && elem_bytes == 2 && mn_total % int64_t(g.box_mn) == 0) {
+    // memory [k_total][mn_total] seen as [group][k][128 bytes]: one copy brings all 64-wide (128-byte)
+    // groups of the tile, landing as consecutive [bk rows x 128 B] blocks — the layout the MMA reads.
+    // Only when MN is a whole number of groups: a partial last group would make the copy read past
+    // the end of the last row.  16-bit operands only: the same 3-D form on 8-bit operands returned
+    // wrong data for the second group at small N on B200, so those keep one 2-D copy per group.
+    g.one_load = 1;
+    return make_tmap_3d(t, ptr, g.box_mn, uint64_t(k_total), uint64_t(mn_total) / g.box_mn,
+                        uint64_t(mn_total) * elem_bytes, 128, g.box_mn, bk, g.boxes);
+  }
   if (!g.mn_major)  // memory [mn_total][k_total], K contiguous
     return make_tmap_2d(t, ptr, uint64_t(k_total), uint64_t(mn_total), uint64_t(k_total) * elem_bytes, bk,
                         uint32_t(tile_mn));
@@ -256,19 +283,22 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
     ta = a.int8 ? ElemType::S8 : ElemType::BF16; tb = a.int8 ? ElemType::U8 : ElemType::BF16;
     fa = 1u; fb = a.int8 ? 0u : 1u;
   }
+  // the pair kernel splits the B tile in halves of bn/2 columns; 8-bit MN-major operands are fetched
+  // in 128-column groups, so their half must be 128 wide
+  const bool pair = cfg.pair && !cfg.swapped && !(a.int8 && cfg.bn != 256);
   p.Mm = int(mn_a);
   p.Nm = int(mn_b);
-  p.tiles_m = ceil_div(mn_a, 128);
+  p.tiles_m = ceil_div(mn_a, pair ? 256 : 128);
   p.tiles_n = ceil_div(mn_b, p.BN);
   p.a = operand_geom(a_mn, 128, eb);
-  p.b = operand_geom(b_mn, p.BN, eb);
-  p.idesc = umma_instr_desc(a.int8 ? 2u : 1u, fa, fb, a_mn ? 1u : 0u, b_mn ? 1u : 0u, 128u, uint32_t(p.BN));
+  p.b = operand_geom(b_mn, pair ? p.BN / 2 : p.BN, eb);
+  p.idesc = umma_instr_desc(a.int8 ? 2u : 1u, fa, fb, a_mn ? 1u : 0u, b_mn ? 1u : 0u, pair ? 256u : 128u, uint32_t(p.BN));
   uint32_t cols = 32;
   while (cols < uint32_t(2 * p.BN)) cols <<= 1;
   p.tmem_cols = cols;
 
   const CUtensorMap tmA = operand_tmap(p.a, ta, eb, pa, mn_a, a.K, 128);
-  const CUtensorMap tmB = operand_tmap(p.b, tb, eb, pb, mn_b, a.K, p.BN);
+  const CUtensorMap tmB = operand_tmap(p.b, tb, eb, pb, mn_b, a.K, pair ? p.BN / 2 : p.BN);
 
   const bool split = cfg.splits > 1;
   void *planes = nullptr;
@@ -300,14 +330,26 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
     p.relu = a.relu;
   }
   const int units = p.tiles_m * p.tiles_n * p.splits;
-  const int grid = std::max(1, std::min(units, cfg.grid > 0 ? cfg.grid : dev.sm_count));
-  const size_t smem = gemm_smem_bytes(p);
-  if (smem > 232448) throw std::invalid_argument("matmul tile configuration exceeds shared memory");
   cudaError_t e;
-  if (!a.int8) e = cfg.swapped ? launch_gemm_kernel<0, true>(tmA, tmB, p, grid, smem, stream)
-                               : launch_gemm_kernel<0, false>(tmA, tmB, p, grid, smem, stream);
-  else         e = cfg.swapped ? launch_gemm_kernel<1, true>(tmA, tmB, p, grid, smem, stream)
-                               : launch_gemm_kernel<1, false>(tmA, tmB, p, grid, smem, stream);
+  if (pair) {
+    // stages are sized for the half B tile: recompute against the shared-memory budget
+    const size_t budget = 232448 - 1024 - 4 * 4096 - 256;
+    p.stages = int(std::max<size_t>(2, std::min<size_t>({size_t(8), budget / (p.a.bytes + p.b.bytes), size_t(std::max(2, p.k_blocks))})));
+    if (a.force && a.force->stages >= 2) p.stages = std::min(p.stages, a.force->stages);
+    const int grid = std::max(2, std::min(2 * units, dev.sm_count & ~1));
+    const size_t smem = gemm_pair_smem_bytes(p);
+    if (smem > 232448) throw std::invalid_argument("matmul tile configuration exceeds shared memory");
+    e = a.int8 ? launch_gemm_pair_kernel<1>(tmA, tmB, p, grid, smem, stream)
+               : launch_gemm_pair_kernel<0>(tmA, tmB, p, grid, smem, stream);
+  } else {
+    const int grid = std::max(1, std::min(units, cfg.grid > 0 ? cfg.grid : dev.sm_count));
+    const size_t smem = gemm_smem_bytes(p);
+    if (smem > 232448) throw std::invalid_argument("matmul tile configuration exceeds shared memory");
+    if (!a.int8) e = cfg.swapped ? launch_gemm_kernel<0, true>(tmA, tmB, p, grid, smem, stream)
+                                 : launch_gemm_kernel<0, false>(tmA, tmB, p, grid, smem, stream);
+    else         e = cfg.swapped ? launch_gemm_kernel<1, true>(tmA, tmB, p, grid, smem, stream)
+                                 : launch_gemm_kernel<1, false>(tmA, tmB, p, grid, smem, stream);
+  }
   if (e != cudaSuccess) throw CudaError(std::string("gemm launch: ") + cudaGetErrorString(e));
   count_launch();
   if (split) {

@@ -24,11 +24,12 @@ class GcB200Error(RuntimeError):
 class MatmulConfig(C.Structure):
     """Mirror of ``gcb200_matmul_config``."""
 
-    _fields_ = [("swapped", _int), ("bn", _int), ("splits", _int), ("stages", _int), ("group_m", _int), ("grid", _int)]
+    _fields_ = [("swapped", _int), ("bn", _int), ("splits", _int), ("stages", _int), ("group_m", _int), ("grid", _int),
+                ("pair", _int)]
 
     def __repr__(self):
         return (f"MatmulConfig(swapped={self.swapped}, bn={self.bn}, splits={self.splits}, stages={self.stages}, "
-                f"group_m={self.group_m}, grid={self.grid})")
+                f"group_m={self.group_m}, grid={self.grid}, pair={self.pair})")
 
 
 _lib = None

@@ -107,6 +107,7 @@ int gcb200_matmul_f32(const float *A, const float *B, const float *bias, float *
  * Pure host logic; needs no device. */
 typedef struct {
   int swapped, bn, splits, stages, group_m, grid;
+  int pair; /* 1: CTA-pair kernel (tcgen05 cta_group::2), 256 x bn tiles on two SMs */
 } gcb200_matmul_config;
 int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count,
                                 gcb200_matmul_config *cfg);
