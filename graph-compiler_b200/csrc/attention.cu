@@ -10,17 +10,21 @@
 // key/value tiles once for both ("two streams"), so that the tensor pipe works
 // on one stream while the other stream's warps are in softmax.
 //
-//   warp 0       TMA producer: Q (once), then K_0, V_0, K_1, V_1, ... into a ring of 32 KiB slots
-//   warp 1       MMA issuer: S_t = Q_t K_j^T and PV_t = P_t V_j (tcgen05.mma, accumulators in TMEM)
-//   warps 2..5   softmax / accumulate / epilogue of stream 0 (one query row per thread)
+//   warp 0       TMA producer: Q (once), then K_0, K_1, V_0, K_2, V_1, ... (the order the MMA warp
+//                consumes them) into a ring of three 32 KiB slots
+//   warp 1       MMA issuer: S_t = Q_t K_j^T and O_t += P_t V_j (tcgen05.mma, S and O in TMEM)
+//   warps 2..5   softmax of stream 0 (one query row per thread)
 //   warps 6..9   the same for stream 1
 //
-// Per key tile and stream: the softmax warps read S from TMEM (row max; then exp2, row sum), write
-// P as bf16 into shared memory in the K-major 128-byte-swizzled layout the MMA reads, the MMA warp
-// issues P V into a fresh TMEM buffer, and the softmax warps fold it into their register
-// accumulators with the usual rescale  O <- (O + PV_{j-1}) * 2^(m_{j-1} - m_j).
+// Per key tile and stream the softmax warps copy the 128 scores of their row from TMEM to registers
+// (which frees S for the next Q K^T at once), take the row maximum, write P = 2^(s*c - m) as bf16 into
+// shared memory in the K-major 128-byte-swizzled layout the MMA reads, and the MMA warp accumulates
+// P V into O, which stays in TMEM for the whole walk.  The reference maximum m is updated lazily:
+// only when the running maximum has grown by more than 8 (a factor 256, harmless in f32 and bf16)
+// is O rescaled in TMEM, so after the first few tiles no thread touches O until the epilogue
+// divides it by the row sum l, which is accumulated with the same m and therefore exact.
 //
-// Shared memory: Q 2 x 32 KiB, K/V ring 3 x 32 KiB, P 2 x 32 KiB = 224 KiB.  TMEM: S0 S1 PV0 PV1,
+// Shared memory: Q 2 x 32 KiB, K/V ring 3 x 32 KiB, P 2 x 32 KiB = 224 KiB.  TMEM: S0 S1 O0 O1,
 // 128 columns each = 512 columns.
 #include "attention.h"
 
@@ -38,6 +42,7 @@ constexpr int kAttThreads = 320;
 constexpr int kTile = 128;          // query rows per stream, key rows per tile
 constexpr int kSlot = 32768;        // one 128 x 128 bf16 tile
 constexpr int kRing = 3;
+constexpr float kLazy = 8.0f;       // rescale O only when the row maximum grew by more than 2^kLazy
 
 struct AttParams {
   int seq, bh, dim;
@@ -52,9 +57,10 @@ struct AttBars {
   uint64_t q_full;
   uint64_t kv_full[kRing];
   uint64_t kv_empty[kRing];
-  uint64_t s_full[2];
-  uint64_t p_ready[2];
-  uint64_t pv_full[2];
+  uint64_t s_full[2];    // MMA -> softmax: S_t holds the scores of the next tile
+  uint64_t s_free[2];    // softmax -> MMA: S_t has been copied to registers
+  uint64_t p_ready[2];   // softmax -> MMA: P_t written, O_t rescaled if needed
+  uint64_t pv_full[2];   // MMA -> softmax: O_t += P_t V_j has retired
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -65,16 +71,11 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// descriptor of K-step `j` (16 elements of the contraction) of a K-major 128 x 128 bf16 tile stored as
-// two 128-row x 128-byte swizzled blocks (contraction index 0..63 in block 0, 64..127 in block 1)
-__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile, int j) {
-  return umma_smem_desc(tile + uint32_t(j >> 2) * 16384u + uint32_t(j & 3) * 32u, 16, 1024);
-}
-// descriptor of K-step `j` (16 key rows) of V [128 keys x 128 d] used as an MN-major B operand:
-// two 64-wide d blocks 16 KiB apart (leading offset), 8-row groups 1 KiB apart (stride offset)
-__device__ __forceinline__ uint64_t v_desc(uint32_t tile, int j) {
-  return umma_smem_desc(tile + uint32_t(j) * 2048u, 16384, 1024);
-}
+// Operand tiles in shared memory.  Q, K and P are K-major 128 x 128 bf16 tiles stored as two 128-row x
+// 128-byte swizzled blocks (contraction index 0..63 in block 0, 64..127 in block 1): K step j starts at
+// block (j >> 2), 32 bytes per step inside it.  V [128 keys x 128 d] is an MN-major B operand: two
+// 64-wide d blocks 16 KiB apart (leading offset), 8-row groups 1 KiB apart (stride offset), 2 KiB
+// per 16-key K step.
 
 __global__ void __launch_bounds__(kAttThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -107,6 +108,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&bars->s_full[t]), 1);
+      mbar_init(smem_u32(&bars->s_free[t]), 4);
       mbar_init(smem_u32(&bars->p_ready[t]), 4);
       mbar_init(smem_u32(&bars->pv_full[t]), 1);
     }
@@ -131,17 +133,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_expect_tx(qf, act1 ? 2 * kSlot : kSlot);
       for (int t = 0; t < (act1 ? 2 : 1); ++t)
         for (int h = 0; h < 2; ++h) tma_load_3d(q_s + t * kSlot + h * 16384, &tmQ, qf, h * 64, q_base0 + t * 128, bh);
-      int err = 0;
-      uint32_t issued = 0;
-      for (int i = 0; i < 2 * n_kv && !err; ++i) {   // i even: K_{i/2}, odd: V_{i/2}
-        const int slot = i % kRing;
-        const uint32_t ph = (i / kRing) & 1u;
-        if (!mbar_wait(smem_u32(&bars->kv_empty[slot]), ph ^ 1u)) { err = ERR_WAIT_EMPTY; break; }
+      int err = 0, slot = 0;
+      uint32_t ph = 0, issued = 0;
+      // one ring entry: wait for the slot, then both 64-wide halves of a 128 x 128 tile
+      auto load = [&](const CUtensorMap *tm, int row0) {
+        if (!mbar_wait(smem_u32(&bars->kv_empty[slot]), ph ^ 1u)) { err = ERR_WAIT_EMPTY; return; }
         const uint32_t full = smem_u32(&bars->kv_full[slot]);
         mbar_expect_tx(full, kSlot);
-        const CUtensorMap *tm = (i & 1) ? &tmV : &tmK;
-        for (int h = 0; h < 2; ++h) tma_load_3d(ring_s + slot * kSlot + h * 16384, tm, full, h * 64, (i >> 1) * kTile, bh);
-        issued = uint32_t(i) + 1;
+        for (int h = 0; h < 2; ++h) tma_load_3d(ring_s + slot * kSlot + h * 16384, tm, full, h * 64, row0, bh);
+        ++issued;
+        if (++slot == kRing) { slot = 0; ph ^= 1u; }
+      };
+      load(&tmK, 0);
+      for (int j = 0; j < n_kv && !err; ++j) {   // consumption order: K_{j+1} before V_j
+        if (j + 1 < n_kv) load(&tmK, (j + 1) * kTile);
+        if (!err) load(&tmV, j * kTile);
       }
       if (err) {
         atomicExch(p.error, err);
@@ -162,159 +168,198 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t idesc_pv = umma_instr_desc(1, 1, 1, 0, 1, 128, 128);   // B (V) MN-major
       const int nt[2] = {n0, n1};
       int err = 0;
-      auto issue_qk = [&](int t, int j, uint32_t kslot) {
+      // This thread's instruction stream is the tensor pipe's critical path: descriptors are split into
+      // a constant high word and a low word (start address in 16-byte units | leading offset << 16)
+      // that advances by a compile-time constant per K step.
+      const uint32_t hi_k = uint32_t(umma_smem_desc(0, 16, 1024) >> 32);
+      const uint32_t hi_v = uint32_t(umma_smem_desc(0, 16384, 1024) >> 32);
+      auto lo_k = [](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); };
+      auto lo_v = [](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1024u << 16); };
+      auto dsc = [](uint32_t lo, uint32_t hi) { return (uint64_t(hi) << 32) | uint64_t(lo); };
+      const uint32_t q_lo[2] = {lo_k(q_s), lo_k(q_s + kSlot)};
+      const uint32_t p_lo[2] = {lo_k(p_s), lo_k(p_s + kSlot)};
+      const uint32_t s_full_b[2] = {smem_u32(&bars->s_full[0]), smem_u32(&bars->s_full[1])};
+      const uint32_t s_free_b[2] = {smem_u32(&bars->s_free[0]), smem_u32(&bars->s_free[1])};
+      const uint32_t p_ready_b[2] = {smem_u32(&bars->p_ready[0]), smem_u32(&bars->p_ready[1])};
+      const uint32_t pv_full_b[2] = {smem_u32(&bars->pv_full[0]), smem_u32(&bars->pv_full[1])};
+      auto issue_qk = [&](int t, uint32_t kslot) {
         const uint32_t d = tmem + uint32_t(t) * 128u;
+        const uint32_t a = q_lo[t], b = lo_k(kslot);
 #pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_f16(d, kmajor_desc(q_s + t * kSlot, s), kmajor_desc(kslot, s), idesc_qk, s > 0 ? 1u : 0u);
-        umma_commit(smem_u32(&bars->s_full[t]));
-        (void)j;
+        for (int s = 0; s < 8; ++s) {
+          const uint32_t off = uint32_t(s >> 2) * 1024u + uint32_t(s & 3) * 2u;
+          umma_f16(d, dsc(a + off, hi_k), dsc(b + off, hi_k), idesc_qk, s > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full_b[t]);
+      };
+      // ring position of the next entry to consume (same order as the producer fills it)
+      int slot = 0;
+      uint32_t ph = 0;
+      auto ring_wait = [&]() { return mbar_wait(smem_u32(&bars->kv_full[slot]), ph); };
+      auto ring_release = [&]() {
+        umma_commit(smem_u32(&bars->kv_empty[slot]));   // free once the MMAs issued so far retire
+        if (++slot == kRing) { slot = 0; ph ^= 1u; }
       };
       if (!mbar_wait(smem_u32(&bars->q_full), 0)) err = ERR_WAIT_FULL;
-      // ring index of K_j is 2j, of V_j is 2j+1
+      if (!err && !ring_wait()) err = ERR_WAIT_FULL;
       if (!err) {
-        if (!mbar_wait(smem_u32(&bars->kv_full[0]), 0)) err = ERR_WAIT_FULL;
         tc_fence_after();
-        if (!err) {
-          for (int t = 0; t < 2; ++t)
-            if (nt[t] > 0) issue_qk(t, 0, ring_s);
-          // K_0 is released when these MMAs retire — unless a later QK of tile 0 is pending (none)
-          umma_commit(smem_u32(&bars->kv_empty[0]));
-        }
+        for (int t = 0; t < 2; ++t)
+          if (nt[t] > 0) issue_qk(t, ring_s + uint32_t(slot) * kSlot);
+        ring_release();
       }
       for (int j = 0; j < n_kv && !err; ++j) {
-        const int iv = 2 * j + 1, ik = 2 * j + 2;          // ring indices of V_j and K_{j+1}
-        const uint32_t vslot = ring_s + (iv % kRing) * kSlot, kslot = ring_s + (ik % kRing) * kSlot;
-        if (!mbar_wait(smem_u32(&bars->kv_full[iv % kRing]), (iv / kRing) & 1u)) { err = ERR_WAIT_FULL; break; }
-        const bool more = (j + 1 < n_kv);
-        if (more && !mbar_wait(smem_u32(&bars->kv_full[ik % kRing]), (ik / kRing) & 1u)) { err = ERR_WAIT_FULL; break; }
-        tc_fence_after();
+        // ---- scores of the next key tile, as soon as each stream has copied its S to registers
+        if (j + 1 < n_kv) {
+          if (!ring_wait()) { err = ERR_WAIT_FULL; break; }
+          const uint32_t kslot = ring_s + uint32_t(slot) * kSlot;
+          for (int t = 0; t < 2 && !err; ++t) {
+            if (j + 1 >= nt[t]) continue;
+            if (!mbar_wait(s_free_b[t], uint32_t(j) & 1u)) { err = ERR_WAIT_TMEM_EMPTY; break; }
+            tc_fence_after();
+            issue_qk(t, kslot);
+          }
+          if (err) break;
+          ring_release();
+        }
+        // ---- O_t += P_t V_j
+        if (!ring_wait()) { err = ERR_WAIT_FULL; break; }
+        const uint32_t v_lo = lo_v(ring_s + uint32_t(slot) * kSlot);
         for (int t = 0; t < 2 && !err; ++t) {
           if (j >= nt[t]) continue;
-          // P_t(j) written and PV_t buffer drained (the softmax warps arrive after both)
-          if (!mbar_wait(smem_u32(&bars->p_ready[t]), uint32_t(j) & 1u)) { err = ERR_WAIT_TMEM_EMPTY; break; }
+          if (!mbar_wait(p_ready_b[t], uint32_t(j) & 1u)) { err = ERR_WAIT_TMEM_EMPTY; break; }
           tc_fence_after();
           const uint32_t d = tmem + 256u + uint32_t(t) * 128u;
+          const uint32_t a = p_lo[t];
 #pragma unroll
-          for (int s = 0; s < 8; ++s)
-            umma_f16(d, kmajor_desc(p_s + t * kSlot, s), v_desc(vslot, s), idesc_pv, s > 0 ? 1u : 0u);
-          umma_commit(smem_u32(&bars->pv_full[t]));
-          if (j + 1 < nt[t]) issue_qk(t, j + 1, kslot);   // S_t is free: its softmax finished before p_ready
+          for (int s = 0; s < 8; ++s) {
+            const uint32_t off = uint32_t(s >> 2) * 1024u + uint32_t(s & 3) * 2u;
+            umma_f16(d, dsc(a + off, hi_k), dsc(v_lo + uint32_t(s) * 128u, hi_v), idesc_pv, (j > 0 || s > 0) ? 1u : 0u);
+          }
+          umma_commit(pv_full_b[t]);
         }
         if (err) break;
-        umma_commit(smem_u32(&bars->kv_empty[iv % kRing]));
-        if (more) umma_commit(smem_u32(&bars->kv_empty[ik % kRing]));
+        ring_release();
       }
       if (err) atomicExch(p.error, err);
     }
   } else {
-    // ---------------------------------------------------------------- softmax / accumulate / epilogue
+    // ---------------------------------------------------------------- softmax / epilogue
     const int t = (warp - 2) >> 2;                  // stream
     const int q = warp & 3;                         // TMEM lane quadrant
     const int row = q * 32 + lane;                  // row within the stream's query tile
     const int q_row = (t == 0 ? q_base0 : q_base1) + row;
     const int nk = (t == 0) ? n0 : n1;
     const uint32_t s_addr = tmem + uint32_t(t) * 128u + (uint32_t(q * 32) << 16);
-    const uint32_t pv_addr = tmem + 256u + uint32_t(t) * 128u + (uint32_t(q * 32) << 16);
-    uint8_t *pbuf = smem + (2 + kRing + t) * kSlot;
+    const uint32_t o_addr = tmem + 256u + uint32_t(t) * 128u + (uint32_t(q * 32) << 16);
+    uint8_t *pbuf = smem + (2 + kRing + t) * kSlot + row * 128;
+    const uint32_t s_full_b = smem_u32(&bars->s_full[t]), s_free_b = smem_u32(&bars->s_free[t]);
+    const uint32_t p_ready_b = smem_u32(&bars->p_ready[t]), pv_full_b = smem_u32(&bars->pv_full[t]);
+    const float c = p.scale_log2e;
 
-    float o[128];
-#pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;   // running max (scaled, log2 domain) and running sum
+    float m_used = -INFINITY;   // reference maximum the exponentials and O currently use (scaled, log2 domain)
+    float l = 0.f;              // running row sum in that reference
     bool dead = false;
 
     for (int j = 0; j < nk && !dead; ++j) {
-      if (!mbar_wait(smem_u32(&bars->s_full[t]), uint32_t(j) & 1u)) {
+      if (!mbar_wait(s_full_b, uint32_t(j) & 1u)) {
         if (lane == 0) atomicExch(p.error, ERR_WAIT_TMEM_FULL);
         dead = true;
         break;
       }
       tc_fence_after();
-      const int kv0 = j * kTile;
+      // ---- the whole score row to registers, then hand S back to the MMA warp
+      uint32_t sv[128];
+      {
+        uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
+        uint32_t(&c1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
+        uint32_t(&c2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[64]);
+        uint32_t(&c3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[96]);
+        tmem_ld_x32(s_addr, c0);
+        tmem_ld_x32(s_addr + 32, c1);
+        tmem_ld_x32(s_addr + 64, c2);
+        tmem_ld_x32(s_addr + 96, c3);
+        tmem_wait_ld();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free_b);
+
       // columns of this tile that take part: inside the sequence and, when causal, not above the diagonal
+      const int kv0 = j * kTile;
       int lim = p.seq - kv0;
       if (p.causal) lim = min(lim, q_row - kv0 + 1);
-      const bool full_tile = lim >= kTile;
-      // ---- pass 1: row maximum
+      if (lim < kTile) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i >= lim) sv[i] = 0xFF800000u;   // -inf
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(s_addr + c * 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(v[i]);
-          mx = (full_tile || c * 32 + i < lim) ? fmaxf(mx, s) : mx;
-        }
-      }
-      const float m_new = fmaxf(m, mx * p.scale_log2e);
-      const float alpha = ex2(m - m_new);           // 0 on the first tile (m = -inf)
-      // ---- fold the previous tile's P V into the accumulator, then rescale
+      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      const float m_tile = mx * c;
+      // lazy reference update: keep the old reference unless the maximum grew by more than 2^kLazy
+      const bool grow = m_tile > m_used + kLazy;
+      const float alpha = grow ? ex2(m_used - m_tile) : 1.f;   // 0 on the first tile (m_used = -inf)
+      if (grow) m_used = m_tile;
+      l *= alpha;
+
       if (j > 0) {
-        if (!mbar_wait(smem_u32(&bars->pv_full[t]), uint32_t(j - 1) & 1u)) {
+        // P_t and O_t are free once the previous P V has retired
+        if (!mbar_wait(pv_full_b, uint32_t(j - 1) & 1u)) {
           if (lane == 0) atomicExch(p.error, ERR_WAIT_TMEM_FULL);
           dead = true;
           break;
         }
         tc_fence_after();
+        if (__any_sync(0xFFFFFFFFu, grow)) {
+          // rescale this warp's 32 rows of O in place (rows that did not grow use alpha = 1)
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 16) {
+            uint32_t v[16];
+            tmem_ld_x16(o_addr + c0, v);
+            tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_x32(pv_addr + c * 32, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(v[i])) * alpha;
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_x16(o_addr + c0, v);
+          }
+          tmem_wait_st();
         }
       }
-      l *= alpha;
-      m = m_new;
-      // ---- pass 2: p = 2^(s*scale*log2e - m), row sum, P -> shared memory (bf16, swizzled K-major)
+      // ---- p = 2^(s*c - m_used), row sum, P -> shared memory (bf16, swizzled K-major)
       float sum = 0.f;
+      const float neg_m = -m_used;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(s_addr + c * 32, v);
-        tmem_wait_ld();
-        uint32_t pk[16];
+      for (int k = 0; k < 16; ++k) {   // sixteen 16-byte chunks of 8 columns
+        uint32_t w[4];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2e, -m));
-          float p1 = ex2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m));
-          if (!full_tile) {
-            p0 = (c * 32 + i < lim) ? p0 : 0.f;
-            p1 = (c * 32 + i + 1 < lim) ? p1 : 0.f;
-          }
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2(fmaf(__uint_as_float(sv[k * 8 + e * 2]), c, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[k * 8 + e * 2 + 1]), c, neg_m));
           sum += p0 + p1;
-pk[i >> 1] = f32_to_bf16_bits(p0) | (f32_to_bf16_bits(p1) << 16);
+          w[e] = pack_bf16x2_rn(p0, p1);
         }
-        // 32 columns = 64 bytes = four 16-byte chunks of block (c >> 1), chunk index (c & 1) * 4 + k
-        uint8_t *blk = pbuf + (c >> 1) * 16384 + row * 128;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int chunk = ((c & 1) * 4 + k) ^ (row & 7);
-          *reinterpret_cast<uint4 *>(blk + chunk * 16) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
-        }
+        // chunk k of the row: block (k >> 3), 16-byte slot (k & 7) ^ (row & 7)
+        *reinterpret_cast<uint4 *>(pbuf + (k >> 3) * 16384 + (((k & 7) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       l += sum;
       fence_proxy_async();     // P visible to the tensor core's shared-memory reads
-      tc_fence_before();       // our TMEM reads of S and PV are ordered before the arrive
+      tc_fence_before();       // TMEM accesses above are ordered before the arrive
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready[t]));
+      if (lane == 0) mbar_arrive(p_ready_b);
     }
     // ---- last P V, normalise, store
     if (!dead && nk > 0) {
-      if (!mbar_wait(smem_u32(&bars->pv_full[t]), uint32_t(nk - 1) & 1u)) {
+      if (!mbar_wait(pv_full_b, uint32_t(nk - 1) & 1u)) {
         if (lane == 0) atomicExch(p.error, ERR_WAIT_TMEM_FULL);
       } else {
         tc_fence_after();
         const float inv = 1.f / l;
         uint16_t *orow = reinterpret_cast<uint16_t *>(p.O) + (size_t(bh) * p.seq + size_t(q_row)) * size_t(p.dim);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c0 = 0; c0 < 4; ++c0) {
           uint32_t v[32];
-          tmem_ld_x32(pv_addr + c * 32, v);
+          tmem_ld_x32(o_addr + c0 * 32, v);
           tmem_wait_ld();
           if (q_row < p.seq) {
 #pragma unroll
@@ -323,11 +368,9 @@ pk[i >> 1] = f32_to_bf16_bits(p0) | (f32_to_bf16_bits(p1) << 16);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int i = k * 8 + e * 2;
-                const float a = (o[c * 32 + i] + __uint_as_float(v[i])) * inv;
-                const float b = (o[c * 32 + i + 1] + __uint_as_float(v[i + 1])) * inv;
-                w[e] = f32_to_bf16_bits(a) | (f32_to_bf16_bits(b) << 16);
+                w[e] = f32_to_bf16_bits(__uint_as_float(v[i]) * inv) | (f32_to_bf16_bits(__uint_as_float(v[i + 1]) * inv) << 16);
               }
-              *reinterpret_cast<uint4 *>(orow + c * 32 + k * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4 *>(orow + c0 * 32 + k * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
         }
