@@ -228,6 +228,25 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    graph_us = None
+    if kind == "cfg1":
+        # latency case: replay a CUDA graph of 50 launches so that host launch cost is not what is timed
+        gr = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(gr, stream=side):
+                for _ in range(50):
+                    fn()
+        torch.cuda.synchronize()
+        gr.replay()
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.record()
+        for _ in range(10):
+            gr.replay()
+        en.record()
+        torch.cuda.synchronize()
+        graph_us = st.elapsed_time(en) / 500 * 1e3
     l0 = lib.launch_count()
     if flush is None:
         st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -251,6 +270,8 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5):
     launches = (lib.launch_count() - l0) // steps
     r = {"case": spec, "ms": ms, "value": work / ms / 1e9, "unit": unit, "launches_per_step": int(launches),
          "l2": "flushed between launches" if flush is not None else "working set larger than L2"}
+    if graph_us is not None:
+        r["us_per_launch_graph_replay"] = graph_us
     if kind == "decode":
         r["roofline"] = {"bound": "hbm", "achieved": bytes_ / ms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": bytes_ / ms / 1e6 / peaks["hbm"]}
@@ -349,8 +370,18 @@ def main():
 
         parallelism = "single GPU"
     else:
+        from gc_b200.tensor_parallel import AllReduceExchange, CudaOps, PeerPushExchange
+
         ws, bs = shard_weights([w.to(dev) for w in W_host], [b.to(dev) for b in B_host], world, rank)
-        tp = TensorParallelMLP(ws, bs, relu=True)
+        exchange, why = None, ""
+        if os.environ.get("GC_B200_EXCHANGE", "peer_push") == "peer_push":
+            try:
+                exchange = PeerPushExchange(BATCH, HIDDEN[-1], dev)
+            except Exception as e:   # symmetric memory unavailable: NCCL all-reduce baseline
+                why = f" (peer push unavailable: {type(e).__name__})"
+        if exchange is None:
+            exchange = AllReduceExchange(CudaOps())
+        tp = TensorParallelMLP(ws, bs, relu=True, exchange=exchange)
         Xd = X_host.to(dev)
         holder = {}
 
@@ -364,7 +395,9 @@ def main():
                 out_host.copy_(y, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
-        parallelism = f"tp{world}: layers 1,3 column-parallel, layers 2,4 row-parallel + f32 all-reduce (NCCL)"
+        parallelism = (f"tp{world}: layers 1,3 column-parallel, layers 2,4 row-parallel, f32 partial sums exchanged by "
+                       + ("GEMM-epilogue peer stores over NVLink + local reduce" if exchange.name == "peer_push"
+                          else "NCCL all-reduce") + why)
     config["parallelism"] = parallelism
 
     def barrier():

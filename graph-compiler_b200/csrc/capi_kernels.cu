@@ -111,7 +111,7 @@ GCB_EXPORT int gcb200_matmul_bf16_cfg(const void *A, const void *B, const void *
     require(!cfg->pair || (!cfg->swapped && cfg->bn % 128 == 0), "the CTA-pair kernel needs bn in {128, 256} and the row-major orientation");
     require(cfg->stages >= 2 && cfg->stages <= 8, "stages must be in [2,8]");
     require(cfg->splits >= 1 && cfg->group_m >= 1, "splits and group_m must be positive");
-    MatmulConfig c{cfg->swapped, cfg->bn, cfg->splits, cfg->stages, cfg->group_m, cfg->grid, cfg->pair};
+    MatmulConfig c{cfg->swapped, cfg->bn, cfg->splits, cfg->stages, cfg->group_m, cfg->grid, cfg->pair, cfg->kpb};
     const int kb = int((K + 63) / 64);
     const int per = (kb + c.splits - 1) / c.splits;
     c.splits = (kb + per - 1) / per;
@@ -129,6 +129,21 @@ GCB_EXPORT int gcb200_matmul_bf16_f32out(const void *A, const void *B, float *Y,
     MatmulArgs a;
     a.A = A; a.B = B; a.M = M; a.N = N; a.K = K; a.trans_a = transpose_a; a.trans_b = transpose_b;
     a.out_kind = OUT_F32; a.out = Y;
+    matmul_tc(a, static_cast<cudaStream_t>(stream));
+  });
+}
+
+GCB_EXPORT int gcb200_matmul_bf16_f32out_push(const void *A, const void *B, void *const *peer_bufs, int n_peers, int my_plane,
+                                              int64_t M, int64_t N, int64_t K, void *stream) {
+  return guarded([&] {
+    require(A && B && peer_bufs && n_peers >= 1 && n_peers <= 8 && my_plane >= 0, "bad arguments");
+    require(M > 0 && N > 0 && K > 0, "matmul dimensions must be positive");
+    for (int d = 0; d < n_peers; ++d) require(peer_bufs[d] && (reinterpret_cast<uintptr_t>(peer_bufs[d]) & 15) == 0, "peer buffers must be 16-byte aligned");
+    if (!(tma_compatible(A, K, 2) && tma_compatible(B, N, 2))) throw std::logic_error("push matmul needs 16-byte aligned operand rows");
+    MatmulArgs a;
+    a.A = A; a.B = B; a.M = M; a.N = N; a.K = K;
+    a.out_kind = OUT_F32; a.out = peer_bufs[0];
+    a.n_peers = n_peers; a.peer_plane = my_plane; a.peer_out = peer_bufs;
     matmul_tc(a, static_cast<cudaStream_t>(stream));
   });
 }
@@ -184,7 +199,7 @@ GCB_EXPORT int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int 
     require(cfg && M > 0 && N > 0 && K > 0 && sm_count > 0, "bad arguments");
     require(dtype_bytes == 1 || dtype_bytes == 2, "dtype_bytes must be 1 or 2");
     MatmulConfig c = select_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count);
-    *cfg = gcb200_matmul_config{c.swapped, c.bn, c.splits, c.stages, c.group_m, c.grid, c.pair};
+    *cfg = gcb200_matmul_config{c.swapped, c.bn, c.splits, c.stages, c.group_m, c.grid, c.pair, c.kpb};
   });
 }
 

@@ -107,7 +107,14 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
         const int gcol = col0 + c * cols_per_chunk;
         if (grow < p.out_rows && gcol < p.out_cols) {
           uint8_t *g = dstp + size_t(grow) * ld_b + size_t(gcol) * es;
-          if (vec_ok && gcol + cols_per_chunk <= p.out_cols) {
+          if (pass == 0 && p.n_peers > 0) {
+            // Row-parallel layer across GPUs: this rank's partial sums go straight from the epilogue
+            // into plane `peer_plane` of every rank's receive buffer (plain stores to peer memory over
+            // NVLink), so the exchange overlaps the tiles still being computed.  Requires full
+            // 16-byte chunks (checked by the launcher).
+            const size_t off = (size_t(p.peer_plane) * size_t(p.out_rows) + size_t(grow)) * ld_b + size_t(gcol) * es;
+            for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[d]) + off) = val;
+          } else if (vec_ok && gcol + cols_per_chunk <= p.out_cols) {
             *reinterpret_cast<uint4 *>(g) = val;
           } else {
             const uint32_t w[4] = {val.x, val.y, val.z, val.w};

@@ -109,8 +109,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int stages = p.stages;
       const uint32_t my_bytes = g.bytes, my_off = is_a ? 0u : p.a.bytes;
       const uint32_t boxes = g.boxes, box_bytes = g.box_bytes, box_mn = g.box_mn;
-      const bool mn = g.mn_major != 0, one = g.one_load != 0;
-      const int bk = p.bk_elems;
+      const bool mn = g.mn_major != 0, one = g.one_load != 0, k3d = g.k3d != 0;
+      const int bk = p.bk_elems, kpb = max(p.kpb, 1);
       int err = 0;
       for (int u = blockIdx.x; u < units && !err; u += gridDim.x) {
         const int tile = u / p.splits, split = u - tile * p.splits;
@@ -120,15 +120,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int kb0 = split * kb_per_split, kb1 = min(p.k_blocks, kb0 + kb_per_split);
         int k_off = kb0 * bk;
         const int grp = mn_off / int(box_mn ? box_mn : 1u);   // 3-D form: index of the first 64-wide MN group
-        for (int kb = kb0; kb < kb1; ++kb, ++it, k_off += bk) {
+        for (int kb = kb0; kb < kb1; kb += kpb, ++it, k_off += bk * kpb) {
           if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u)) { err = ERR_WAIT_EMPTY; break; }
           const uint32_t full = smem_u32(&bars->full[s]);
           mbar_expect_tx(full, my_bytes);
           const uint32_t dst = base + uint32_t(s) * stage_bytes + my_off;
-          if (!mn) tma_load_2d(dst, tm, full, k_off, mn_off);
-          else if (one) tma_load_3d(dst, tm, full, 0, k_off, grp);
-          else
+          if (!mn) {
+            if (k3d) tma_load_3d(dst, tm, full, 0, mn_off, kb);
+            else
+              for (uint32_t i = 0; i < boxes; ++i) tma_load_2d(dst + i * box_bytes, tm, full, k_off + int(i) * bk, mn_off);
+          } else if (one) {
+            tma_load_3d(dst, tm, full, 0, k_off, grp);
+          } else {
             for (uint32_t i = 0; i < boxes; ++i) tma_load_2d(dst + i * box_bytes, tm, full, mn_off + int(i * box_mn), k_off);
+          }
           if (++s == stages) { s = 0; ph ^= 1u; }
         }
       }
@@ -156,6 +161,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t a_hi = uint32_t(adesc0 >> 32), b_hi = uint32_t(bdesc0 >> 32);
       const uint32_t a_lo0 = uint32_t(adesc0), b_lo0 = uint32_t(bdesc0);
       const uint32_t stage_step = stage_bytes >> 4, a_k = p.a.kstep >> 4, b_k = p.b.kstep >> 4;
+      const uint32_t a_sub = p.a.sub_step >> 4, b_sub = p.b.sub_step >> 4;   // next K block inside a stage
+      const int kpb = max(p.kpb, 1);
       const uint32_t idesc = p.idesc;
       const int stages = p.stages;
       auto desc = [](uint32_t lo, uint32_t hi) { return (uint64_t(hi) << 32) | uint64_t(lo); };
@@ -171,20 +178,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * uint32_t(p.BN);
         uint32_t accum = 0;   // the first MMA of a tile overwrites the accumulator (zero-init at the first K block)
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += kpb) {
           if (!mbar_wait(smem_u32(&bars->full[s]), ph)) { err = ERR_WAIT_FULL; break; }
           tc_fence_after();
-          const uint32_t al = a_lo0 + uint32_t(s) * stage_step, bl = b_lo0 + uint32_t(s) * stage_step;
-          if (KIND == 0) {
-            umma_f16(d_tmem, desc(al, a_hi), desc(bl, b_hi), idesc, accum);
-            umma_f16(d_tmem, desc(al + a_k, a_hi), desc(bl + b_k, b_hi), idesc, 1u);
-            umma_f16(d_tmem, desc(al + 2 * a_k, a_hi), desc(bl + 2 * b_k, b_hi), idesc, 1u);
-            umma_f16(d_tmem, desc(al + 3 * a_k, a_hi), desc(bl + 3 * b_k, b_hi), idesc, 1u);
-          } else {
-            umma_i8(d_tmem, desc(al, a_hi), desc(bl, b_hi), idesc, accum);
-            umma_i8(d_tmem, desc(al + a_k, a_hi), desc(bl + b_k, b_hi), idesc, 1u);
-            umma_i8(d_tmem, desc(al + 2 * a_k, a_hi), desc(bl + 2 * b_k, b_hi), idesc, 1u);
-            umma_i8(d_tmem, desc(al + 3 * a_k, a_hi), desc(bl + 3 * b_k, b_hi), idesc, 1u);
+          uint32_t al = a_lo0 + uint32_t(s) * stage_step, bl = b_lo0 + uint32_t(s) * stage_step;
+#pragma unroll 1
+          for (int sub = 0; sub < kpb; ++sub, al += a_sub, bl += b_sub) {
+            if (KIND == 0) {
+              umma_f16(d_tmem, desc(al, a_hi), desc(bl, b_hi), idesc, accum);
+              umma_f16(d_tmem, desc(al + a_k, a_hi), desc(bl + b_k, b_hi), idesc, 1u);
+              umma_f16(d_tmem, desc(al + 2 * a_k, a_hi), desc(bl + 2 * b_k, b_hi), idesc, 1u);
+              umma_f16(d_tmem, desc(al + 3 * a_k, a_hi), desc(bl + 3 * b_k, b_hi), idesc, 1u);
+            } else {
+              umma_i8(d_tmem, desc(al, a_hi), desc(bl, b_hi), idesc, accum);
+              umma_i8(d_tmem, desc(al + a_k, a_hi), desc(bl + b_k, b_hi), idesc, 1u);
+              umma_i8(d_tmem, desc(al + 2 * a_k, a_hi), desc(bl + 2 * b_k, b_hi), idesc, 1u);
+              umma_i8(d_tmem, desc(al + 3 * a_k, a_hi), desc(bl + 3 * b_k, b_hi), idesc, 1u);
+            }
+            accum = 1u;
           }
           accum = 1u;
           umma_commit(smem_u32(&bars->empty[s]));   // stage reusable once these MMAs retire

@@ -27,8 +27,11 @@ struct OperandGeom {
   uint32_t lbo, sbo;   // descriptor leading / stride byte offsets
   uint32_t kstep;      // bytes to advance the start address per MMA K step
   uint32_t bytes;      // bytes per stage
-  uint32_t one_load;   // 1: the whole stage arrives with ONE TMA instruction (K-major: a 2-D box;
-                       //    MN-major: a 3-D box over [64-wide MN group][K][group index])
+  uint32_t one_load;   // 1: the whole stage arrives with ONE TMA instruction (K-major: a 2-D box, or a
+                       //    3-D box over [128-byte K block][MN][K block index] when a stage holds several K
+                       //    blocks; MN-major: a 3-D box over [128-byte MN group][K][group index])
+  uint32_t k3d;        // K-major only: the tensor map is the 3-D form (coordinates 0, mn, K block)
+  uint32_t sub_step;   // descriptor bytes from one K block of a stage to the next
 };
 
 struct GemmParams {
@@ -41,6 +44,7 @@ struct GemmParams {
   int splits;           // split-K factor (1 = none)
   int bk_elems;         // elements per K block (128 bytes worth)
   int stages;
+  int kpb;              // K blocks (of 128 bytes) per pipeline stage
   int group_m;          // rasterisation: tiles_m rows walked per column sweep
   OperandGeom a, b;
   uint32_t idesc;
@@ -58,6 +62,10 @@ struct GemmParams {
   long long ld_dump;
   int relu;
   int out_rows, out_cols; // logical output extent (for edge predication)
+  // peer push (row-parallel layers): when n_peers > 0 the f32 tile is stored into plane `peer_plane`
+  // of each of peer_out[0..n_peers) (buffers of [planes][out_rows][ld_out] f32) instead of `out`
+  int n_peers, peer_plane;
+  void *peer_out[8];
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
 };
 

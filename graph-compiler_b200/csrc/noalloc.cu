@@ -129,6 +129,7 @@ GCB_EXPORT int gcb200_matmul_bf16_splitk_static(const void *A, const void *B, co
     p.k_blocks = k_blocks;
     p.splits = cfg.splits;
     p.stages = cfg.stages;
+    p.kpb = 1;
     p.group_m = cfg.group_m;
     p.BN = cfg.bn;
     p.out_rows = int(M);

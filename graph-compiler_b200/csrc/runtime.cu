@@ -136,35 +136,49 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
     c.bn = std::max(16, ceil_div(M, 16) * 16);
     tiles = ceil_div(N, 128);
   } else {
-    // Largest tile whose wave quantisation loses least; ties go to the larger
-    // tile (more operand reuse per byte staged in shared memory).
-    const int cand[3] = {256, 128, 64};
-    double best = -1.0;
-    int best_bn = 256;
+    // Time model fitted to measurements on B200 (microseconds): a CTA spends c per 128-byte K block —
+    // dominated by the per-stage hand-shake, so it shrinks little with the tile and a lot when a
+    // stage carries two K blocks (possible while three stages still fit: bn <= 128) — plus a fixed
+    // cost per tile; a split-K run adds the traffic of its partial planes and a second launch.
+    //   measured per K block at 8192^3 / 16384^3: bn 256: 0.42;  bn 128: 0.38 (one block per stage),
+    //   0.27 (two);  bn 64: 0.29 (one)
+    const int cand[4] = {256, 192, 128, 64};
+    const int split_cand[6] = {1, 2, 3, 4, 6, 8};
+    double best_t = 1e30;
+    int best_bn = 256, best_sp = 1, best_kpb = 1;
     for (int bn : cand) {
       if (bn % out_gran) continue;
       int bn_eff = bn;
       if (N < bn) bn_eff = std::max(out_gran, ceil_div(N, out_gran) * out_gran);
+      const int kpb = (bn_eff <= 128 && k_blocks >= 4) ? 2 : 1;
+      const double c_kb = bn_eff >= 256 ? 0.42 : bn_eff >= 192 ? 0.40 : bn_eff >= 128 ? (kpb == 2 ? 0.27 : 0.38)
+                                                                                      : (kpb == 2 ? 0.21 : 0.29) * std::max(0.6, bn_eff / 64.0);
       const int t = ceil_div(M, 128) * ceil_div(N, bn_eff);
-      const int waves = ceil_div(t, sm_count);
-      const double useful = double(M) * double(N) / (double(waves) * sm_count * 128.0 * bn_eff);
-      const double reuse = bn_eff >= 256 ? 1.0 : (bn_eff >= 128 ? 0.72 : 0.50); // measured: 804 / 582 TFLOPS at 4096^3
-      const double score = useful * reuse;
-      if (score > best + 1e-9) { best = score; best_bn = bn_eff; }
+      for (int sp : split_cand) {
+        if (sp > 1 && (k_blocks < 16 * sp || t >= sm_count)) continue;
+        const int kbs = ceil_div(k_blocks, sp);
+        if (sp > 1 && kbs % kpb) continue;   // a stage must not straddle two splits
+        const int waves = ceil_div(t * sp, sm_count);
+        double us = waves * (kbs * c_kb + 3.0);
+        if (sp > 1) us += 4.0 + (2.0 * sp * double(M) * double(N) * 4.0 + double(M) * double(N) * out_bytes) / 1.5e6;
+        if (us < best_t - 1e-9) { best_t = us; best_bn = bn_eff; best_sp = sp; best_kpb = kpb; }
+      }
     }
     c.bn = best_bn;
+    c.splits = best_sp;
+    c.kpb = best_kpb;
     tiles = ceil_div(M, 128) * ceil_div(N, c.bn);
   }
-  // split-K only when the tile grid leaves most SMs idle and K is deep
-  c.splits = 1;
-  if (tiles * 2 <= sm_count && k_blocks >= 16) {
-    int s = std::min({sm_count / tiles, k_blocks / 8, 32});
-    if (c.swapped) s = std::min({(2 * sm_count + tiles - 1) / tiles, k_blocks / 8, 32});
-    c.splits = std::max(1, s);
-  } else if (c.swapped && k_blocks >= 16) {
-    // decode shapes stream the weights once: keep every SM busy with >= 2 units
-    int s = std::min({(3 * sm_count + tiles - 1) / tiles, k_blocks / 8, 32});
-    c.splits = std::max(1, s);
+  if (c.swapped) {
+    // decode shapes stream the weights once (measured at M=16, K=8192, N=28672: 5.5 TB/s with two K
+    // blocks per stage and no split, 4.8 with one): split K only when there are fewer tiles than SMs
+    c.kpb = k_blocks >= 4 ? 2 : 1;
+    c.splits = 1;
+    if (tiles < sm_count && k_blocks >= 32) {
+      int sp = std::max(1, std::min({(sm_count + tiles - 1) / tiles, k_blocks / 16, 32}));
+      while (sp > 1 && ceil_div(k_blocks, sp) % c.kpb) --sp;
+      c.splits = sp;
+    }
   }
   // every split must own at least one K block
   {
@@ -181,15 +195,17 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
     b_bytes = std::max(mn, km);
   }
   const size_t budget = 232448 - 1024 - 4 * 4096 - 256;
-  c.stages = int(std::min<size_t>(8, budget / (a_bytes + b_bytes)));
-  c.stages = std::max(2, std::min(c.stages, std::max(2, k_blocks)));
+  const int kpb_eff = std::max(1, c.kpb);
+  c.stages = int(std::min<size_t>(8, budget / ((a_bytes + b_bytes) * size_t(kpb_eff))));
+  c.stages = std::max(2, std::min(c.stages, std::max(2, ceil_div(k_blocks, kpb_eff))));
   c.group_m = 8;
   c.grid = std::min(tiles * c.splits, sm_count);
   if (const char *ov = std::getenv("GC_B200_TILE")) {
     // "bn,splits,stages,group_m" — any field may be 0 to keep the heuristic's choice
-    int bn = 0, sp = 0, st = 0, gm = 0, pr = -1;
-    if (std::sscanf(ov, "%d,%d,%d,%d,%d", &bn, &sp, &st, &gm, &pr) >= 1) {
+    int bn = 0, sp = 0, st = 0, gm = 0, pr = -1, kp = 0;
+    if (std::sscanf(ov, "%d,%d,%d,%d,%d,%d", &bn, &sp, &st, &gm, &pr, &kp) >= 1) {
       if (pr >= 0) c.pair = pr;
+      if (kp > 0) c.kpb = kp;
       if (bn > 0 && !c.swapped) c.bn = bn;
       if (sp > 0) { const int per = ceil_div(k_blocks, sp); c.splits = ceil_div(k_blocks, per); }
       if (st > 0) c.stages = std::min(st, c.stages);
@@ -202,49 +218,63 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
 }
 
 // ----------------------------------------------------------------------------- matmul planning
-OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes) {
+OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes, int kpb) {
   OperandGeom g{};
-  const uint32_t bk = 128 / elem_bytes;  // K elements per stage
+  const uint32_t bk = 128 / elem_bytes;  // K elements per 128-byte K block
   g.mn_major = mn_major ? 1u : 0u;
   if (!mn_major) {
-    g.boxes = 1;
+    // [K block][MN row][128 B]: each K block is its own swizzled [tile_mn x 128 B] tile
+    g.boxes = uint32_t(kpb);
     g.box_bytes = uint32_t(tile_mn) * 128u;
     g.box_mn = uint32_t(tile_mn);
     g.lbo = 16;
     g.sbo = 1024;
     g.kstep = 32;
-    g.bytes = g.box_bytes;
-    g.one_load = 1;
+    g.sub_step = g.box_bytes;
+    g.bytes = g.boxes * g.box_bytes;
+    g.one_load = kpb == 1 ? 1u : 0u;
   } else {
+    // [MN group][K row][128 B]: the K blocks of a stage are consecutive rows of every group
     g.box_mn = 128 / elem_bytes;
     g.boxes = (uint32_t(tile_mn) + g.box_mn - 1) / g.box_mn;
-    g.box_bytes = bk * 128u;
+    g.box_bytes = bk * uint32_t(kpb) * 128u;
     g.lbo = g.box_bytes;
     g.sbo = 1024;
     g.kstep = (32u / elem_bytes) * 128u;
+    g.sub_step = bk * 128u;
     g.bytes = g.boxes * g.box_bytes;
   }
   return g;
 }
 
 CUtensorMap operand_tmap(OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
-                                int64_t k_total, int tile_mn) {
+                                int64_t k_total, int tile_mn, int kpb) {
   const uint32_t bk = 128 / elem_bytes;
   if (g.mn_major && elem_bytes == 2 && mn_total % int64_t(g.box_mn) == 0) {
     // memory [k_total][mn_total] seen as [group][k][128 bytes]: one copy brings all 64-wide (128-byte)
-    // groups of the tile, landing as consecutive [bk rows x 128 B] blocks — the layout the MMA reads.
+    // groups of the tile, landing as consecutive [rows x 128 B] blocks — the layout the MMA reads.
     // Only when MN is a whole number of groups: a partial last group would make the copy read past
     // the end of the last row.  16-bit operands only: the same 3-D form on 8-bit operands returned
     // wrong data for the second group at small N on B200, so those keep one 2-D copy per group.
     g.one_load = 1;
     return make_tmap_3d(t, ptr, g.box_mn, uint64_t(k_total), uint64_t(mn_total) / g.box_mn,
-                        uint64_t(mn_total) * elem_bytes, 128, g.box_mn, bk, g.boxes);
+                        uint64_t(mn_total) * elem_bytes, 128, g.box_mn, bk * uint32_t(kpb), g.boxes);
   }
-  if (!g.mn_major)  // memory [mn_total][k_total], K contiguous
+  if (!g.mn_major) {  // memory [mn_total][k_total], K contiguous
+    if (kpb > 1 && elem_bytes == 2 && k_total % int64_t(bk) == 0) {
+      // [K block][mn][128 bytes]: one copy brings the stage's K blocks as consecutive swizzled tiles.
+      // Only when K is a whole number of blocks (a partial block would read into the next row).
+      g.one_load = 1;
+      g.k3d = 1;
+      return make_tmap_3d(t, ptr, bk, uint64_t(mn_total), uint64_t(k_total) / bk, uint64_t(k_total) * elem_bytes, 128, bk,
+                          uint32_t(tile_mn), uint32_t(kpb));
+    }
     return make_tmap_2d(t, ptr, uint64_t(k_total), uint64_t(mn_total), uint64_t(k_total) * elem_bytes, bk,
                         uint32_t(tile_mn));
+  }
   // memory [k_total][mn_total], MN contiguous
-  return make_tmap_2d(t, ptr, uint64_t(mn_total), uint64_t(k_total), uint64_t(mn_total) * elem_bytes, g.box_mn, bk);
+  return make_tmap_2d(t, ptr, uint64_t(mn_total), uint64_t(k_total), uint64_t(mn_total) * elem_bytes, g.box_mn,
+                      bk * uint32_t(kpb));
 }
 
 void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
@@ -290,16 +320,34 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   p.Nm = int(mn_b);
   p.tiles_m = ceil_div(mn_a, pair ? 256 : 128);
   p.tiles_n = ceil_div(mn_b, p.BN);
-  p.a = operand_geom(a_mn, 128, eb);
-  p.b = operand_geom(b_mn, pair ? p.BN / 2 : p.BN, eb);
+  // K blocks per stage: only the one-CTA kernel, and with split-K only when every split is a whole
+  // number of stages (a stage must not straddle two splits)
+  int kpb = (pair || cfg.kpb < 1) ? 1 : cfg.kpb;
+  {
+    const int per = ceil_div(p.k_blocks, p.splits);
+    if (p.splits > 1 && per % kpb) kpb = 1;
+    if (kpb > p.k_blocks) kpb = 1;
+  }
+  p.kpb = kpb;
+  p.a = operand_geom(a_mn, 128, eb, kpb);
+  p.b = operand_geom(b_mn, pair ? p.BN / 2 : p.BN, eb, kpb);
   p.idesc = umma_instr_desc(a.int8 ? 2u : 1u, fa, fb, a_mn ? 1u : 0u, b_mn ? 1u : 0u, pair ? 256u : 128u, uint32_t(p.BN));
   uint32_t cols = 32;
   while (cols < uint32_t(2 * p.BN)) cols <<= 1;
   p.tmem_cols = cols;
 
-  const CUtensorMap tmA = operand_tmap(p.a, ta, eb, pa, mn_a, a.K, 128);
-  const CUtensorMap tmB = operand_tmap(p.b, tb, eb, pb, mn_b, a.K, pair ? p.BN / 2 : p.BN);
+  const CUtensorMap tmA = operand_tmap(p.a, ta, eb, pa, mn_a, a.K, 128, kpb);
+  const CUtensorMap tmB = operand_tmap(p.b, tb, eb, pb, mn_b, a.K, pair ? p.BN / 2 : p.BN, kpb);
 
+  if (a.n_peers > 0) {
+    if (a.out_kind != OUT_F32 || cfg.swapped || a.n_peers > 8 || (a.N % 4) != 0 || a.ld_out)
+      throw std::invalid_argument("peer push needs the f32-out row-major form, N % 4 == 0 and at most 8 peers");
+    cfg.splits = 1;
+    p.splits = 1;
+    p.n_peers = a.n_peers;
+    p.peer_plane = a.peer_plane;
+    for (int d = 0; d < a.n_peers; ++d) p.peer_out[d] = a.peer_out[d];
+  }
   const bool split = cfg.splits > 1;
   void *planes = nullptr;
   if (split) {
@@ -343,6 +391,13 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
                : launch_gemm_pair_kernel<0>(tmA, tmB, p, grid, smem, stream);
   } else {
     const int grid = std::max(1, std::min(units, cfg.grid > 0 ? cfg.grid : dev.sm_count));
+    {
+      const size_t budget = 232448 - 1024 - 4 * 4096 - 256;
+      const int fit = int(budget / (p.a.bytes + p.b.bytes));
+      if (fit < 2) throw std::invalid_argument("matmul stage does not fit twice in shared memory");
+      p.stages = std::max(2, std::min({p.stages, fit, std::max(2, ceil_div(p.k_blocks, kpb))}));
+      if (kpb > 1) p.stages = std::min(8, fit);
+    }
     const size_t smem = gemm_smem_bytes(p);
     if (smem > 232448) throw std::invalid_argument("matmul tile configuration exceeds shared memory");
     if (!a.int8) e = cfg.swapped ? launch_gemm_kernel<0, true>(tmA, tmB, p, grid, smem, stream)

@@ -56,6 +56,7 @@ struct MatmulConfig {
   int group_m;   // rasterisation group
   int grid;      // CTAs launched (persistent)
   int pair;      // 1: CTA-pair kernel (256 x bn tiles, two SMs per tile)
+  int kpb;       // K blocks of 128 bytes per pipeline stage (0 or 1: one)
 };
 // dtype_bytes: 2 (bf16) or 1 (int8).  out_bytes: bytes per output element written by the GEMM kernel.
 MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
@@ -64,10 +65,10 @@ bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes);
 
 // Shared-memory stage geometry and tensor map of one GEMM operand tile (`tile_mn` rows of the MMA
 // M or N side; K contiguous in memory unless mn_major).
-OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes);
+OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes, int kpb = 1);
 // (sets g.one_load when the operand can be fetched with a single 3-D copy per stage)
 CUtensorMap operand_tmap(OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
-                         int64_t k_total, int tile_mn);
+                         int64_t k_total, int tile_mn, int kpb = 1);
 CUtensorMap make_tmap_3d(ElemType t, const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                          uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
 
@@ -87,6 +88,9 @@ struct MatmulArgs {
   const int32_t *comp = nullptr;
   int32_t *acc_dump = nullptr;
   int relu = 0;
+  int n_peers = 0;              // > 0: push the f32 result into plane `peer_plane` of each peer buffer
+  int peer_plane = 0;
+  void *const *peer_out = nullptr;
   const MatmulConfig *force = nullptr; // optional override
   void *scratch = nullptr;      // optional caller-provided split-K scratch (else the device workspace)
   size_t scratch_bytes = 0;

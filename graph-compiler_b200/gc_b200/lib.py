@@ -25,11 +25,11 @@ class MatmulConfig(C.Structure):
     """Mirror of ``gcb200_matmul_config``."""
 
     _fields_ = [("swapped", _int), ("bn", _int), ("splits", _int), ("stages", _int), ("group_m", _int), ("grid", _int),
-                ("pair", _int)]
+                ("pair", _int), ("kpb", _int)]
 
     def __repr__(self):
         return (f"MatmulConfig(swapped={self.swapped}, bn={self.bn}, splits={self.splits}, stages={self.stages}, "
-                f"group_m={self.group_m}, grid={self.grid}, pair={self.pair})")
+                f"group_m={self.group_m}, grid={self.grid}, pair={self.pair}, kpb={self.kpb})")
 
 
 _lib = None
@@ -54,6 +54,7 @@ def load() -> C.CDLL:
         "gcb200_matmul_bf16": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
         "gcb200_matmul_bf16_cfg": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig), _vp],
         "gcb200_matmul_bf16_f32out": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
+        "gcb200_matmul_bf16_f32out_push": [_vp, _vp, C.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp],
         "gcb200_reduce_bias_act_bf16": [_vp, _int, _i64, _vp, _vp, _i64, _i64, _int, _vp],
         "gcb200_matmul_u8s8": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp],
         "gcb200_colsum_s8": [_vp, _vp, _i64, _i64, _i32, _vp],
@@ -144,6 +145,14 @@ def matmul_bf16_f32out(A, B, transpose_a=False, transpose_b=False, out=None):
     check(load().gcb200_matmul_bf16_f32out(_ptr(A), _ptr(B), _ptr(out), M, N, K, int(transpose_a), int(transpose_b),
                                            _stream()))
     return out
+
+
+def matmul_bf16_f32out_push(A, B, peer_ptrs, my_plane: int):
+    """f32 partial sums of A.B stored into plane ``my_plane`` of every buffer in ``peer_ptrs`` (ints)."""
+    M, K = A.shape
+    N = B.shape[1]
+    arr = (_vp * len(peer_ptrs))(*peer_ptrs)
+    check(load().gcb200_matmul_bf16_f32out_push(_ptr(A), _ptr(B), arr, len(peer_ptrs), my_plane, M, N, K, _stream()))
 
 
 def reduce_bias_act_bf16(parts, bias=None, relu=False, out=None):

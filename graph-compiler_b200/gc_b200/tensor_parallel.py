@@ -46,7 +46,7 @@ def shard_weights(weights: Sequence, biases: Sequence, world: int, rank: int):
 
 
 class CudaOps:
-    """The three launchers a step needs, bound to the C ABI."""
+    """The launchers a step needs, bound to the C ABI."""
 
     def __init__(self):
         from . import lib
@@ -59,30 +59,83 @@ class CudaOps:
     def linear_partial(self, x, w):
         return self._lib.matmul_bf16_f32out(x, w)
 
-    def epilogue(self, partial, b, relu):
-        return self._lib.reduce_bias_act_bf16(partial.unsqueeze(0), b, relu=relu)
+    def epilogue(self, planes, b, relu):
+        """planes: f32 [nparts, M, N] — summed in plane order, then cast, bias, ReLU."""
+        return self._lib.reduce_bias_act_bf16(planes, b, relu=relu)
+
+
+class AllReduceExchange:
+    """Baseline exchange: local f32 partial sums, then one NCCL/gloo all-reduce."""
+
+    name = "all_reduce"
+    launches_per_pair = 3
+
+    def __init__(self, ops, group=None):
+        self.ops, self.group = ops, group
+
+    def partial_planes(self, x, w):
+        import torch.distributed as dist
+
+        part = self.ops.linear_partial(x, w)
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+        return part.unsqueeze(0)
+
+
+class PeerPushExchange:
+    """Fused exchange: the GEMM epilogue stores this rank's partial sums into plane `rank` of every
+    rank's receive buffer (peer-mapped symmetric memory, plain NVLink stores), one cross-rank barrier,
+    then every rank reduces its g planes locally in rank order.  Two receive buffers alternate so that
+    a buffer is only overwritten after the barrier of the following exchange, i.e. after every rank has
+    finished reading it."""
+
+    name = "peer_push"
+    launches_per_pair = 3
+
+    def __init__(self, M: int, N: int, device, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import lib
+
+        self._lib = lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.bufs, self.hdls, self.ptrs = [], [], []
+        for _ in range(2):
+            t = symm.empty((self.world, M, N), dtype=torch.float32, device=device)
+            h = symm.rendezvous(t, self.group)
+            self.bufs.append(t)
+            self.hdls.append(h)
+            self.ptrs.append([int(p) for p in h.buffer_ptrs])
+        self.turn = 0
+
+    def partial_planes(self, x, w):
+        i = self.turn
+        self.turn ^= 1
+        self._lib.matmul_bf16_f32out_push(x, w, self.ptrs[i], self.rank)
+        self.hdls[i].barrier(channel=0)   # every rank's stores have landed and are visible
+        return self.bufs[i]
 
 
 class TensorParallelMLP:
     """An even number of bias+ReLU layers, sharded as described in the module docstring."""
 
-    def __init__(self, weight_shards: List, bias_shards: List, relu: bool = True, ops=None, group=None):
+    def __init__(self, weight_shards: List, bias_shards: List, relu: bool = True, ops=None, group=None, exchange=None):
         if len(weight_shards) % 2:
             raise ValueError("tensor-parallel MLP needs an even number of layers (column then row)")
         self.w, self.b, self.relu = list(weight_shards), list(bias_shards), relu
         self.ops = ops if ops is not None else CudaOps()
         self.group = group
-        self.launches_per_step = 3 * (len(self.w) // 2)
+        self.exchange = exchange if exchange is not None else AllReduceExchange(self.ops, group)
+        self.launches_per_step = self.exchange.launches_per_pair * (len(self.w) // 2)
         self.collectives_per_step = len(self.w) // 2
 
     def step(self, x):
-        import torch.distributed as dist
-
         h = x
         for i in range(0, len(self.w), 2):
             h = self.ops.linear(h, self.w[i], self.b[i], self.relu)          # column-parallel, local post-ops
-            part = self.ops.linear_partial(h, self.w[i + 1])                 # row-parallel, f32 partial sums
-            if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-                dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
-            h = self.ops.epilogue(part, self.b[i + 1], self.relu)            # cast, bias, ReLU after the reduce
+            planes = self.exchange.partial_planes(h, self.w[i + 1])          # row-parallel f32 partial sums, exchanged
+            h = self.ops.epilogue(planes, self.b[i + 1], self.relu)          # reduce, cast, bias, ReLU
         return h

@@ -71,6 +71,16 @@ int gcb200_matmul_bf16(const void *A, const void *B, const void *bias, void *Y, 
 int gcb200_matmul_bf16_f32out(const void *A, const void *B, float *Y, int64_t M, int64_t N, int64_t K,
                               int transpose_a, int transpose_b, void *stream);
 
+/* Row-parallel layer across GPUs, compute and exchange in one kernel: the f32 partial sums
+ * A.B of this rank are written by the GEMM epilogue, tile by tile, into plane `my_plane` of EVERY
+ * buffer in peer_bufs[0..n_peers) — device pointers to [planes][M][N] f32 buffers, one per rank,
+ * peer-mapped (e.g. symmetric memory), this rank's own included.  Plain stores over NVLink; no
+ * multicast loads.  After a cross-rank barrier every rank holds all partial planes and finishes with
+ * gcb200_reduce_bias_act_bf16 (planes summed in rank order, so every rank gets identical bits).
+ * The across-device form of the reference's K-split (DeepTileContractionOp.cpp:446-471). */
+int gcb200_matmul_bf16_f32out_push(const void *A, const void *B, void *const *peer_bufs, int n_peers, int my_plane,
+                                   int64_t M, int64_t N, int64_t K, void *stream);
+
 /* Sum `nparts` f32 planes [M,N] (`plane_stride` elements apart) in plane order,
  * then apply the bf16 epilogue bf16(bf16(sum)+bias), ReLU.  The reduce + cast
  * step of the K-split form (DeepTileContractionOp.cpp:446-471). */
@@ -108,6 +118,7 @@ int gcb200_matmul_f32(const float *A, const float *B, const float *bias, float *
 typedef struct {
   int swapped, bn, splits, stages, group_m, grid;
   int pair; /* 1: CTA-pair kernel (tcgen05 cta_group::2), 256 x bn tiles on two SMs */
+  int kpb;  /* K blocks of 128 bytes per pipeline stage (0 or 1: one) */
 } gcb200_matmul_config;
 int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count,
                                 gcb200_matmul_config *cfg);

@@ -175,8 +175,12 @@ def test_tile_selection_for_the_benchmark_shapes():
     sel = lambda M, N, K, db=2, ob=2: lib.select_matmul_config(M, N, K, db, ob, 148)
     c = sel(8192, 8192, 8192)
     assert (c.swapped, c.bn, c.splits) == (0, 256, 1) and c.grid == 148
-    c = sel(16, 28672, 8192)            # decode shape: weights on the MMA M side, split-K to fill the SMs
-    assert c.swapped == 1 and c.bn == 16 and c.splits > 1
+    c = sel(16, 28672, 8192)            # decode shape: weights on the MMA M side, two K blocks per stage
+    assert c.swapped == 1 and c.bn == 16 and c.splits == 1 and c.kpb == 2
+    c = sel(16, 512, 8192)              # few weight tiles: split K to fill the SMs
+    assert c.swapped == 1 and c.splits > 1 and (8192 // 64 // c.splits) % c.kpb == 0
+    c = sel(512, 4096, 16384)           # one wave of 128-wide tiles, two K blocks per stage
+    assert (c.bn, c.kpb, c.splits) == (128, 2, 1)
     c = sel(128, 256, 512)              # BASELINE configs[0]
     assert c.swapped == 0 and c.bn in (64, 128, 256)
     c = sel(1024, 4096, 4096, 1, 4)     # int8

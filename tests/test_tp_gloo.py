@@ -33,8 +33,8 @@ class OracleOps:
         _, acc = oracle.linear_bf16(_bits(x), _bits(w), return_acc=True)
         return torch.from_numpy(acc)
 
-    def epilogue(self, partial, b, relu):
-        return _from_bits(oracle.reduce_epilogue_bf16(partial.numpy()[None], None if b is None else _bits(b), relu=relu))
+    def epilogue(self, planes, b, relu):
+        return _from_bits(oracle.reduce_epilogue_bf16(planes.numpy(), None if b is None else _bits(b), relu=relu))
 
 
 def _make(exact: bool):
