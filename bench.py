@@ -170,7 +170,7 @@ def cpu_onednn_class(rows=BATCH):
 
 
 # --------------------------------------------------------------------------------------- other BASELINE configs
-def run_case(spec: str, steps: int = 20, warmup: int = 5):
+def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "auto"):
     """Time one kernel-level case with device-resident inputs (CUDA events on the launching stream).
 
     spec: gemm:M:N:K | decode | int8:M:N:K | attention:B:H:S:D:causal(0|1) | cfg1
@@ -224,6 +224,8 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5):
         l2_flush = bytes_ < 256e6
     else:
         raise ValueError(spec)
+    if flush_mode != "auto":
+        l2_flush = flush_mode == "on"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if l2_flush else None
     for _ in range(warmup):
         fn()
@@ -299,6 +301,8 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="also time the other BASELINE configs (extra key 'sweep')")
     ap.add_argument("--case", default=None, help="time ONE kernel-level case instead (see run_case) and print its line; "
                                                   "used for ncu captures of a single kernel")
+    ap.add_argument("--flush", default="auto", choices=["auto", "on", "off"],
+                    help="--case only: write a 256 MiB buffer between timed launches (auto: when the working set is below 256 MB)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
 
@@ -326,7 +330,7 @@ def main():
         import torch
 
         torch.cuda.set_device(local_rank)
-        print(json.dumps(run_case(a.case, a.steps, a.warmup)))
+        print(json.dumps(run_case(a.case, a.steps, a.warmup, a.flush)))
         return
 
     import torch

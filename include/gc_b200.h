@@ -74,8 +74,8 @@ int gcb200_matmul_bf16_f32out(const void *A, const void *B, float *Y, int64_t M,
 /* Row-parallel layer across GPUs, compute and exchange in one kernel: the f32 partial sums
  * A.B of this rank are written by the GEMM epilogue, tile by tile, into plane `my_plane` of EVERY
  * buffer in peer_bufs[0..n_peers) — device pointers to [planes][M][N] f32 buffers, one per rank,
- * peer-mapped (e.g. symmetric memory), this rank's own included.  Plain stores over NVLink; no
- * multicast loads.  After a cross-rank barrier every rank holds all partial planes and finishes with
+ * peer-mapped (e.g. symmetric memory), this rank's own included.  Plain stores over NVLink, no
+ * loads from a peer.  After a cross-rank barrier every rank holds all partial planes and finishes with
  * gcb200_reduce_bias_act_bf16 (planes summed in rank order, so every rank gets identical bits).
  * The across-device form of the reference's K-split (DeepTileContractionOp.cpp:446-471). */
 int gcb200_matmul_bf16_f32out_push(const void *A, const void *B, void *const *peer_bufs, int n_peers, int my_plane,
