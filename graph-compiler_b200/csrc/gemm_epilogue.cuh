@@ -14,123 +14,150 @@ template <int KIND, bool SWAPPED>
 __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t t_addr, int row0, int nn0, int split,
                                                    int q, int lane, uint8_t *stg) {
   const int mm = row0 + q * 32 + lane;   // MMA row of this thread
-      if (!SWAPPED) {
-  // ---- MMA row = output row.  Work in slabs of 128 output bytes per row.
-  const int row = mm;
-  const bool two_byte = (p.out_kind == OUT_BF16);
-  const int slab_cols = two_byte ? 64 : 32;
-  uint8_t *outp = reinterpret_cast<uint8_t *>(p.out);
-  const size_t esz = two_byte ? 2 : 4;
-  const size_t plane = (p.splits > 1) ? size_t(split) * size_t(p.split_stride) : 0;
-  for (int c0 = 0; c0 < p.BN; c0 += slab_cols) {
-    uint32_t v[64];
-    {
-      uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);
-      tmem_ld_x32(t_addr + c0, lo);
+  if (!SWAPPED) {
+    // ---- MMA row = output row.  Work in slabs of 128 output bytes per row, in two phases per slab:
+    //  row phase    each thread owns one row: accumulators from TMEM, the first rounding (bf16 outputs),
+    //               16-byte chunks into the warp's swizzled staging buffer;
+    //  store phase  each thread owns one 16-byte chunk position (lane & 7) of rows (lane >> 3) + 4 i: its
+    //               4 or 8 output columns are the same for all eight rows, so bias / scale / compensation
+    //               are loaded once per slab, applied here, and the warp stores full 128-byte row segments.
+    const bool two_byte = (p.out_kind == OUT_BF16);
+    const int slab_cols = two_byte ? 64 : 32;
+    const size_t esz = two_byte ? 2 : 4;
+    const size_t plane = (p.splits > 1) ? size_t(split) * size_t(p.split_stride) : 0;
+    uint8_t *dstp = reinterpret_cast<uint8_t *>(p.out) + plane * esz;
+    const size_t ld_b = size_t(p.ld_out) * esz;
+    const bool vec_ok = ((ld_b & 15) == 0) && ((reinterpret_cast<uintptr_t>(dstp) & 15) == 0);
+    const bool dump = (KIND == 1) && p.acc_dump != nullptr;
+    const bool dump_vec = dump && ((size_t(p.ld_dump) & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.acc_dump) & 15) == 0);
+    const int chunk = lane & 7, rsub = lane >> 3;
+    const int cpc = two_byte ? 8 : 4;   // columns per 16-byte chunk
+    const bool late_bf16 = two_byte && p.bias_kind == BIAS_BF16;   // bias (and ReLU) applied in the store phase
+    for (int c0 = 0; c0 < p.BN; c0 += slab_cols) {
+      const int col0 = nn0 + c0;
+      if (col0 >= p.out_cols) break;   // the rest of the tile lies beyond the last output column
+      // ------------------------------------------------------------ row phase
+      uint32_t v[64];
+      {
+        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);
+        tmem_ld_x32(t_addr + c0, lo);
+        if (two_byte) {
+          uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[32]);
+          tmem_ld_x32(t_addr + c0 + 32, hi);
+        }
+        tmem_wait_ld();
+      }
       if (two_byte) {
-        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[32]);
-        tmem_ld_x32(t_addr + c0 + 32, hi);
-      }
-      tmem_wait_ld();
-    }
-    uint4 packed[8];
-    const int col0 = nn0 + c0;
-    if (p.out_kind == OUT_BF16) {
-      uint32_t h[64];
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        uint32_t y = f32_to_bf16_bits(__uint_as_float(v[j]));
-        const int col = col0 + j;
-        if (p.bias_kind == BIAS_BF16 && col < p.out_cols) {
-          const uint32_t b = reinterpret_cast<const uint16_t *>(p.bias)[col];
-          y = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(y), bf16_bits_to_f32(b)));
-        }
-        if (p.relu) {
-          const float f = bf16_bits_to_f32(y);
-          y = (f != f) ? y : (f > 0.f ? y : 0u);
-        }
-        h[j] = y;
-      }
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        packed[c] = make_uint4(h[8 * c] | (h[8 * c + 1] << 16), h[8 * c + 2] | (h[8 * c + 3] << 16),
-                               h[8 * c + 4] | (h[8 * c + 5] << 16), h[8 * c + 6] | (h[8 * c + 7] << 16));
-    } else {
-      uint32_t o[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = col0 + j;
-        if (p.out_kind == OUT_DEQUANT_F32) {
-          float f = 0.f;
-          if (col < p.out_cols) {
-            const int32_t a = int32_t(v[j]) - (p.comp ? p.comp[col] : 0);
-            f = __fmul_rn(float(a), p.scale[col]);
-            if (p.bias_kind == BIAS_F32) f = __fadd_rn(f, reinterpret_cast<const float *>(p.bias)[col]);
-            if (p.relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
+          for (int e = 0; e < 4; ++e) {
+            uint32_t y0 = f32_to_bf16_bits(__uint_as_float(v[8 * c + 2 * e]));
+            uint32_t y1 = f32_to_bf16_bits(__uint_as_float(v[8 * c + 2 * e + 1]));
+            if (p.relu && !late_bf16) {
+              const float f0 = bf16_bits_to_f32(y0), f1 = bf16_bits_to_f32(y1);
+              y0 = (f0 != f0) ? y0 : (f0 > 0.f ? y0 : 0u);
+              y1 = (f1 != f1) ? y1 : (f1 > 0.f ? y1 : 0u);
+            }
+            w[e] = y0 | (y1 << 16);
           }
-          o[j] = __float_as_uint(f);
-        } else if (p.out_kind == OUT_F32) {
-          float f = __uint_as_float(v[j]);
-          if (p.bias_kind == BIAS_F32 && col < p.out_cols)
-            f = __fadd_rn(f, reinterpret_cast<const float *>(p.bias)[col]);
-          if (p.relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
-          o[j] = __float_as_uint(f);
-        } else {
-          o[j] = v[j];
+          *reinterpret_cast<uint4 *>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4 *>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+              make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      }
+      __syncwarp();
+      // ------------------------------------------------------------ store phase
+      const int gcol = col0 + chunk * cpc;
+      const int nvalid = min(cpc, p.out_cols - gcol);   // <= 0: this chunk is beyond the last column
+      uint32_t bias_b[8];
+      float bias_f[4], scale_f[4];
+      int32_t comp_i[4];
+      if (late_bf16) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bias_b[e] = (e < nvalid) ? reinterpret_cast<const uint16_t *>(p.bias)[gcol + e] : 0u;
+      }
+      if (!two_byte) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const bool in = e < nvalid;
+          bias_f[e] = (in && p.bias_kind == BIAS_F32) ? reinterpret_cast<const float *>(p.bias)[gcol + e] : 0.f;
+          scale_f[e] = (in && p.out_kind == OUT_DEQUANT_F32) ? p.scale[gcol + e] : 1.f;
+          comp_i[e] = (in && p.out_kind == OUT_DEQUANT_F32 && p.comp) ? p.comp[gcol + e] : 0;
         }
       }
-#pragma unroll
-      for (int c = 0; c < 8; ++c) packed[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
-    }
-    // two passes when the raw accumulators are dumped as well
-    const int passes = (p.acc_dump != nullptr && KIND == 1) ? 2 : 1;
-    for (int pass = 0; pass < passes; ++pass) {
-      if (pass == 1) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) packed[c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-      }
-      uint8_t *dstp = pass == 0 ? outp + plane * esz : reinterpret_cast<uint8_t *>(p.acc_dump);
-      const size_t ld_b = pass == 0 ? size_t(p.ld_out) * esz : size_t(p.ld_dump) * 4;
-      const size_t es = pass == 0 ? esz : 4;
-      const int cols_per_chunk = int(16 / es);
-      // stage: row = lane, 16-byte chunk c at position c ^ (lane & 7)
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4 *>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) = packed[c];
-      __syncwarp();
-      const bool vec_ok = ((ld_b & 15) == 0) && ((reinterpret_cast<uintptr_t>(dstp) & 15) == 0);
 #pragma unroll
       for (int itr = 0; itr < 8; ++itr) {
-        const int r = itr * 4 + (lane >> 3), c = lane & 7;
-        const uint4 val = *reinterpret_cast<const uint4 *>(stg + r * 128 + ((c ^ (r & 7)) << 4));
+        const int r = itr * 4 + rsub;
+        const uint4 raw = *reinterpret_cast<const uint4 *>(stg + r * 128 + ((chunk ^ (r & 7)) << 4));
         const int grow = row0 + q * 32 + r;
-        const int gcol = col0 + c * cols_per_chunk;
-        if (grow < p.out_rows && gcol < p.out_cols) {
-          uint8_t *g = dstp + size_t(grow) * ld_b + size_t(gcol) * es;
-          if (pass == 0 && p.n_peers > 0) {
-            // Row-parallel layer across GPUs: this rank's partial sums go straight from the epilogue
-            // into plane `peer_plane` of every rank's receive buffer (plain stores to peer memory over
-            // NVLink), so the exchange overlaps the tiles still being computed.  Requires full
-            // 16-byte chunks (checked by the launcher).
-            const size_t off = (size_t(p.peer_plane) * size_t(p.out_rows) + size_t(grow)) * ld_b + size_t(gcol) * es;
-            for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[d]) + off) = val;
-          } else if (vec_ok && gcol + cols_per_chunk <= p.out_cols) {
-            *reinterpret_cast<uint4 *>(g) = val;
-          } else {
-            const uint32_t w[4] = {val.x, val.y, val.z, val.w};
-            const int nvalid = min(cols_per_chunk, p.out_cols - gcol);
-            for (int e = 0; e < nvalid; ++e) {
-              if (es == 2) reinterpret_cast<uint16_t *>(g)[e] = uint16_t(w[e >> 1] >> ((e & 1) * 16));
-              else         reinterpret_cast<uint32_t *>(g)[e] = w[e];
+        if (grow >= p.out_rows || nvalid <= 0) continue;
+        uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        if (late_bf16) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint32_t y[2] = {w[e] & 0xFFFFu, w[e] >> 16};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t t = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(y[h]), bf16_bits_to_f32(bias_b[2 * e + h])));
+              if (p.relu) {
+                const float f = bf16_bits_to_f32(t);
+                t = (f != f) ? t : (f > 0.f ? t : 0u);
+              }
+              y[h] = t;
             }
+            w[e] = y[0] | (y[1] << 16);
+          }
+        } else if (p.out_kind == OUT_DEQUANT_F32) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float f = __fmul_rn(float(int32_t(w[e]) - comp_i[e]), scale_f[e]);
+            if (p.bias_kind == BIAS_F32) f = __fadd_rn(f, bias_f[e]);
+            if (p.relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
+            w[e] = __float_as_uint(f);
+          }
+        } else if (p.out_kind == OUT_F32) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float f = __uint_as_float(w[e]);
+            if (p.bias_kind == BIAS_F32) f = __fadd_rn(f, bias_f[e]);
+            if (p.relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
+            w[e] = __float_as_uint(f);
+          }
+        }
+        const uint4 val = make_uint4(w[0], w[1], w[2], w[3]);
+        uint8_t *g = dstp + size_t(grow) * ld_b + size_t(gcol) * esz;
+        if (p.n_peers > 0) {
+          // Row-parallel layer across GPUs: this rank's partial sums go straight from the epilogue
+          // into plane `peer_plane` of every rank's receive buffer (plain stores to peer memory over
+          // NVLink), so the exchange overlaps the tiles still being computed.  Requires full
+          // 16-byte chunks (checked by the launcher).
+          const size_t off = (size_t(p.peer_plane) * size_t(p.out_rows) + size_t(grow)) * ld_b + size_t(gcol) * esz;
+          for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[d]) + off) = val;
+        } else if (vec_ok && nvalid == cpc) {
+          *reinterpret_cast<uint4 *>(g) = val;
+        } else {
+          for (int e = 0; e < nvalid; ++e) {
+            if (two_byte) reinterpret_cast<uint16_t *>(g)[e] = uint16_t(w[e >> 1] >> ((e & 1) * 16));
+            else          reinterpret_cast<uint32_t *>(g)[e] = w[e];
+          }
+        }
+        if (dump) {   // raw s32 accumulators beside the dequantised result
+          int32_t *dg = p.acc_dump + size_t(grow) * size_t(p.ld_dump) + size_t(gcol);
+          if (dump_vec && nvalid == 4) *reinterpret_cast<uint4 *>(dg) = raw;
+          else {
+            const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+            for (int e = 0; e < nvalid; ++e) dg[e] = int32_t(rw[e]);
           }
         }
       }
       __syncwarp();
     }
-    (void)row;
-  }
-} else {
+  } else {
   // ---- swapped orientation: MMA row = output column (this thread),
   //      MMA column = output row.  A warp stores 32 consecutive output
   //      columns of one output row per instruction.

@@ -96,9 +96,31 @@ def _pack(tensors: Dict[int, object], order=None):
     return arr, keep
 
 
+class BoundCall:
+    """An execute call with its tensor structs built once: what a C caller does when it runs the same
+    partition on the same buffers every step (the structs of dnnl_graph_compiler_execute are plain
+    caller-owned memory, src/dnnl/dnnl_graph_compiler.cpp:214-226)."""
+
+    def __init__(self, exe: "Executable", inputs, outputs):
+        self._exe = exe
+        self._i, self._ki = _pack(inputs)
+        self._o, self._ko = _pack(outputs)
+        self._bufs = (inputs, outputs)   # keep the arrays alive
+        self._fn = _bind().dnnl_graph_compiler_execute
+
+    def run(self) -> None:
+        st = self._fn(self._exe._h, self._i, self._o)
+        if st != SUCCESS:
+            raise DnnlError(st, _lib.load().gcb200_last_error().decode(errors="replace"))
+
+
 class Executable:
     def __init__(self, handle):
         self._h = handle
+
+    def bind(self, inputs: Dict[int, object], outputs: Dict[int, object]) -> BoundCall:
+        """Build the argument structs once; ``.run()`` then only makes the C call."""
+        return BoundCall(self, inputs, outputs)
 
     def execute(self, inputs: Dict[int, object], outputs: Dict[int, object]) -> None:
         """Synchronous, like the reference: results are in ``outputs`` on return."""

@@ -51,6 +51,12 @@ def test_basic_workflow_add():
                                             "outputs": [_t(2, "f32", [128])]}]}))
     exe.execute({1: b, 0: a}, {2: out})   # order differs from the argument order: matched by id
     assert np.array_equal(out, a + b)
+    # the same call with its tensor structs built once: new data in the same buffers is picked up
+    bound = exe.bind({0: a, 1: b}, {2: out})
+    for k in (2.0, 3.0):
+        a[1] = k
+        bound.run()
+        assert np.array_equal(out, a + b)
 
 
 def test_ops_div_mul_sub():

@@ -89,5 +89,8 @@ def test_tensor_parallel_mlp_on_gpus(mode):
     for r in range(world):
         for step in range(3):
             assert np.array_equal(res[r][step], res[0][0]), (r, step)   # every rank, every step: identical bits
-    mx, same = assert_bf16_close(res[0][0], want, max(HIDDEN), what=f"tp {mode}", floor_div=1.0)
+    # last layer: bf16(bf16(acc) + bias) rounds twice; |acc| <= |result| + |bias| bounds the pre-bias value
+    from _util import bf16_f32
+    pre = np.abs(bf16_f32(want)) + np.abs(bf16_f32(_bits(Bs[3])))[None, :]
+    mx, same = assert_bf16_close(res[0][0], want, max(HIDDEN), what=f"tp {mode}", floor_div=1.0, pre=pre)
     print(f"tp{world} {mode}: max_abs={mx:.4g} bit-identical={same:.5f}")
