@@ -206,4 +206,76 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
 }
 }
 
+// TMA-store form of the row-major epilogue (bf16 with optional bias / ReLU, or raw f32 / s32 planes).
+// Each thread owns one accumulator row: TMEM -> registers -> rounding and post-ops on packed pairs ->
+// 16-byte chunks into a swizzled 32 x 128-byte staging slab -> one cp.async.bulk.tensor store per slab
+// issued by lane 0.  Two staging slabs per warp alternate, so the copy engine drains one while the
+// warp fills the other; rows and columns beyond the output are clipped by the copy engine.
+// stg: this warp's two 4 KiB slabs (1 KiB aligned); buf: slab to fill next (kept by the caller across tiles).
+template <int KIND>
+__device__ __forceinline__ void gemm_epilogue_tile_tma(const GemmParams &p, uint32_t t_addr, int row0, int nn0, int split,
+                                                       int q, int lane, uint8_t *stg, uint32_t &buf) {
+  const bool two_byte = (p.out_kind == OUT_BF16);
+  const int slab_cols = two_byte ? 64 : 32;
+  const int grow0 = row0 + q * 32;
+  const bool rows_in = grow0 < p.out_rows;
+  for (int c0 = 0; c0 < p.BN; c0 += slab_cols) {
+    const int col0 = nn0 + c0;
+    if (col0 >= p.out_cols) break;
+    uint32_t v[64];
+    {
+      uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);
+      tmem_ld_x32(t_addr + c0, lo);
+      if (two_byte) {
+        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[32]);
+        tmem_ld_x32(t_addr + c0 + 32, hi);
+      }
+    }
+    // the slab filled two stores ago must have been read by the copy engine before it is overwritten
+    if (lane == 0) tma_store_wait_read<1>();
+    uint32_t bias2 = 0;   // bias of columns col0 + 2 lane, + 1 (bf16 pair), handed round by shuffles
+    if (two_byte && p.bias_kind == BIAS_BF16) {
+      const int c = col0 + 2 * lane;
+      const uint16_t *b = reinterpret_cast<const uint16_t *>(p.bias);
+      const uint32_t b0 = c < p.out_cols ? b[c] : 0u, b1 = c + 1 < p.out_cols ? b[c + 1] : 0u;
+      bias2 = b0 | (b1 << 16);
+    }
+    tmem_wait_ld();
+    __syncwarp();
+    uint8_t *slab = stg + buf * 4096u;
+    if (two_byte) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 4 * c + e;   // pair index: columns 2j, 2j + 1 of the slab
+          uint32_t y = pack_bf16x2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));   // first rounding
+          if (p.bias_kind == BIAS_BF16) {
+            const uint32_t bb = __shfl_sync(0xFFFFFFFFu, bias2, j);
+            const float f0 = __fadd_rn(__uint_as_float(y << 16), __uint_as_float(bb << 16));
+            const float f1 = __fadd_rn(__uint_as_float(y & 0xFFFF0000u), __uint_as_float(bb & 0xFFFF0000u));
+            y = pack_bf16x2_rn(f0, f1);                                                             // second rounding
+          }
+          if (p.relu) y = bf16x2_relu(y);
+          w[e] = bf16x2_fix_nan(y);
+        }
+        *reinterpret_cast<uint4 *>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4 *>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+            make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    }
+    fence_proxy_async();   // generic-proxy writes of the slab -> visible to the copy engine
+    __syncwarp();
+    if (lane == 0 && rows_in) {
+      tma_store_3d(&p.tmC, smem_u32(slab), col0, grow0, split);
+      tma_store_commit();
+    }
+    buf ^= 1u;
+  }
+}
+
 } // namespace gcb

@@ -27,7 +27,7 @@ namespace gcb {
 
 constexpr int kThreads = 224;
 constexpr int kBM = 128;             // MMA M (cta_group::1)
-constexpr int kStageStaging = 4096;  // per epilogue warp: 32 rows x 128 B
+constexpr int kStageStaging = 8192;  // per epilogue warp: two slabs of 32 rows x 128 B
 constexpr int kMaxStages = 8;
 
 struct SmemBarriers {
@@ -211,6 +211,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     uint8_t *stg = staging + (warp - 2) * kStageStaging;
     uint32_t tcount = 0;
+    uint32_t slab = 0;   // TMA-store form: staging slab to fill next
     bool dead = false;
     for (int u = blockIdx.x; u < units && !dead; u += gridDim.x, ++tcount) {
       const int tile = u / p.splits, split = u - tile * p.splits;
@@ -226,11 +227,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t t_addr = tmem_base + acc * uint32_t(p.BN) + (uint32_t(q * 32) << 16);
       const int nn0 = tn * p.BN;                 // first MMA column of the tile
 
-      gemm_epilogue_tile<KIND, SWAPPED>(p, t_addr, tm * kBM, nn0, split, q, lane, stg);
+      if (!SWAPPED && p.tma_store) gemm_epilogue_tile_tma<KIND>(p, t_addr, tm * kBM, nn0, split, q, lane, stg, slab);
+      else gemm_epilogue_tile<KIND, SWAPPED>(p, t_addr, tm * kBM, nn0, split, q, lane, stg);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
     }
+    // the staging slabs must outlive the copy engine's reads, the stores must land before the grid ends
+    if (!SWAPPED && p.tma_store && lane == 0) tma_store_wait<0>();
   }
 
   // ---------------------------------------------------------------------- tear-down

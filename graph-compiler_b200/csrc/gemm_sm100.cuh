@@ -67,6 +67,11 @@ struct GemmParams {
   int n_peers, peer_plane;
   void *peer_out[8];
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
+  // TMA-store epilogue (one-CTA kernel, row-major orientation): tmC covers the output as
+  // [planes][rows][cols] with a box of {128 bytes of columns, 32 rows, 1}; each epilogue warp hands its
+  // 32 x 128-byte slabs to the copy engine instead of storing them itself.
+  int tma_store;
+  CUtensorMap tmC;
 };
 
 // KIND: 0 = bf16 x bf16 -> f32, 1 = u8 x s8 -> s32.  SWAPPED: MMA rows are output columns.

@@ -106,7 +106,10 @@ CUtensorMap make_tmap_2d(ElemType t, const void *ptr, uint64_t inner, uint64_t o
 CUtensorMap make_tmap_3d(ElemType t, const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                          uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2) {
   CUtensorMap m;
-  CUtensorMapDataType dt = (t == ElemType::BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUtensorMapDataType dt = (t == ElemType::BF16)  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : (t == ElemType::F32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : (t == ElemType::S32) ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                                  : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {b0, b1, b2};
@@ -194,7 +197,7 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
     const size_t km = size_t(c.bn) * 128;
     b_bytes = std::max(mn, km);
   }
-  const size_t budget = 232448 - 1024 - 4 * 4096 - 256;
+  const size_t budget = 232448 - 1024 - 4 * 8192 - 256;
   const int kpb_eff = std::max(1, c.kpb);
   c.stages = int(std::min<size_t>(8, budget / ((a_bytes + b_bytes) * size_t(kpb_eff))));
   c.stages = std::max(2, std::min(c.stages, std::max(2, ceil_div(k_blocks, kpb_eff))));
@@ -377,11 +380,24 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
     p.ld_dump = a.N;
     p.relu = a.relu;
   }
+  // TMA-store epilogue: bf16 outputs (bias / ReLU applied in registers) and raw f32 / s32 planes, when the
+  // copy engine can address the output (16-byte aligned base and row pitch)
+  if (!pair && !cfg.swapped && a.n_peers == 0 && p.acc_dump == nullptr) {
+    const int esz = p.out_kind == OUT_BF16 ? 2 : 4;
+    const bool plain = p.out_kind == OUT_BF16 ? (p.bias_kind == BIAS_NONE || p.bias_kind == BIAS_BF16)
+                                              : ((p.out_kind == OUT_F32 || p.out_kind == OUT_S32) && p.bias_kind == BIAS_NONE && !p.relu);
+    if (plain && tma_compatible(p.out, p.ld_out, esz) && (!split || (size_t(p.split_stride) * esz) % 16 == 0)) {
+      const ElemType ct = p.out_kind == OUT_BF16 ? ElemType::BF16 : (p.out_kind == OUT_S32 ? ElemType::S32 : ElemType::F32);
+      p.tmC = make_tmap_3d(ct, p.out, uint64_t(a.N), uint64_t(a.M), uint64_t(std::max(1, p.splits)), uint64_t(p.ld_out) * esz,
+                           split ? uint64_t(p.split_stride) * esz : uint64_t(a.M) * uint64_t(p.ld_out) * esz, 128 / esz, 32, 1);
+      p.tma_store = 1;
+    }
+  }
   const int units = p.tiles_m * p.tiles_n * p.splits;
   cudaError_t e;
   if (pair) {
     // stages are sized for the half B tile: recompute against the shared-memory budget
-    const size_t budget = 232448 - 1024 - 4 * 4096 - 256;
+    const size_t budget = 232448 - 1024 - 4 * 8192 - 256;
     p.stages = int(std::max<size_t>(2, std::min<size_t>({size_t(8), budget / (p.a.bytes + p.b.bytes), size_t(std::max(2, p.k_blocks))})));
     if (a.force && a.force->stages >= 2) p.stages = std::min(p.stages, a.force->stages);
     const int grid = std::max(2, std::min(2 * units, dev.sm_count & ~1));
@@ -392,7 +408,7 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   } else {
     const int grid = std::max(1, std::min(units, cfg.grid > 0 ? cfg.grid : dev.sm_count));
     {
-      const size_t budget = 232448 - 1024 - 4 * 4096 - 256;
+      const size_t budget = 232448 - 1024 - 4 * 8192 - 256;
       const int fit = int(budget / (p.a.bytes + p.b.bytes));
       if (fit < 2) throw std::invalid_argument("matmul stage does not fit twice in shared memory");
       p.stages = std::max(2, std::min({p.stages, fit, std::max(2, ceil_div(p.k_blocks, kpb))}));

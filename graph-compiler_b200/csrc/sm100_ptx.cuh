@@ -324,4 +324,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
   return r;
 }
 
+// cvt.rn.bf16x2 returns 0x7FFF for a NaN input; the reference conversion returns 0x7FC0
+// (BrgemmInterface.h:83-92).  Patch the (rare) NaN halves of a packed pair.
+__device__ __forceinline__ uint32_t bf16x2_fix_nan(uint32_t w) {
+  const uint32_t t = w & 0x7FFF7FFFu;
+  if (((t + 0x00010001u) & 0x80008000u) != 0u) {
+    if ((w & 0x7FFFu) == 0x7FFFu) w = (w & 0xFFFF0000u) | 0x7FC0u;
+    if ((w & 0x7FFF0000u) == 0x7FFF0000u) w = (w & 0x0000FFFFu) | 0x7FC00000u;
+  }
+  return w;
+}
+// max(x, +0) on a packed pair, NaN propagating (arith.maximumf): the NaN comes back canonical and is
+// patched by bf16x2_fix_nan.
+__device__ __forceinline__ uint32_t bf16x2_relu(uint32_t w) {
+  uint32_t r;
+  asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(0u));
+  return r;
+}
+
 } // namespace gcb
