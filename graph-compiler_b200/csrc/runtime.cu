@@ -144,7 +144,7 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
     // stage carries two K blocks (possible while three stages still fit: bn <= 128) — plus a fixed
     // cost per tile; a split-K run adds the traffic of its partial planes and a second launch.
     //   measured per K block at 8192^3 / 16384^3: bn 256: 0.42;  bn 128: 0.38 (one block per stage),
-    //   0.27 (two);  bn 64: 0.29 (one)
+    //   0.277 (two);  bn 64: 0.29 (one)
     const int cand[4] = {256, 192, 128, 64};
     const int split_cand[6] = {1, 2, 3, 4, 6, 8};
     double best_t = 1e30;
@@ -154,7 +154,7 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
       int bn_eff = bn;
       if (N < bn) bn_eff = std::max(out_gran, ceil_div(N, out_gran) * out_gran);
       const int kpb = (bn_eff <= 128 && k_blocks >= 4) ? 2 : 1;
-      const double c_kb = bn_eff >= 256 ? 0.42 : bn_eff >= 192 ? 0.40 : bn_eff >= 128 ? (kpb == 2 ? 0.27 : 0.38)
+      const double c_kb = bn_eff >= 256 ? 0.42 : bn_eff >= 192 ? 0.40 : bn_eff >= 128 ? (kpb == 2 ? 0.277 : 0.38)
                                                                                       : (kpb == 2 ? 0.21 : 0.29) * std::max(0.6, bn_eff / 64.0);
       const int t = ceil_div(M, 128) * ceil_div(N, bn_eff);
       for (int sp : split_cand) {
@@ -163,7 +163,9 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
         if (sp > 1 && kbs % kpb) continue;   // a stage must not straddle two splits
         const int waves = ceil_div(t * sp, sm_count);
         double us = waves * (kbs * c_kb + 3.0);
-        if (sp > 1) us += 4.0 + (2.0 * sp * double(M) * double(N) * 4.0 + double(M) * double(N) * out_bytes) / 1.5e6;
+        // partial planes written and read back (f32), the result written, one more launch:
+        // measured 13 us for 2 planes of 512 x 4096
+        if (sp > 1) us += 3.0 + (2.0 * sp * double(M) * double(N) * 4.0 + double(M) * double(N) * out_bytes) / 3.5e6;
         if (us < best_t - 1e-9) { best_t = us; best_bn = bn_eff; best_sp = sp; best_kpb = kpb; }
       }
     }

@@ -179,7 +179,9 @@ def test_tile_selection_for_the_benchmark_shapes():
     assert c.swapped == 1 and c.bn == 16 and c.splits == 1 and c.kpb == 2
     c = sel(16, 512, 8192)              # few weight tiles: split K to fill the SMs
     assert c.swapped == 1 and c.splits > 1 and (8192 // 64 // c.splits) % c.kpb == 0
-    c = sel(512, 4096, 16384)           # one wave of 128-wide tiles, two K blocks per stage
+    c = sel(512, 4096, 16384)           # 64 tiles of 128 x 256: K split in two fills 128 SMs
+    assert (c.bn, c.kpb, c.splits) == (256, 1, 2)
+    c = sel(512, 4096, 4096)            # one wave of 128-wide tiles, two K blocks per stage
     assert (c.bn, c.kpb, c.splits) == (128, 2, 1)
     c = sel(128, 256, 512)              # BASELINE configs[0]
     assert c.swapped == 0 and c.bn in (64, 128, 256)
