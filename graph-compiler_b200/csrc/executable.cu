@@ -20,6 +20,7 @@
 #include "../../include/gc_b200.h"
 #include "attention.h"
 #include "graph.h"
+#include "memplan.h"
 #include "runtime.h"
 #include "sm100_ptx.cuh"
 
@@ -538,6 +539,43 @@ GCB_EXPORT int gcb200_plan_dump(const dnnl_graph_compiler_executable *exe, char 
     buf[n] = '\0';
   }
   return GCB200_OK;
+}
+
+GCB_EXPORT int gcb200_schedule_memory(const uint64_t *trace_buffer, const uint64_t *trace_size, int n_traces,
+                                      uint64_t alignment, int hot_first, const uint64_t *hint_buffer,
+                                      const uint64_t *hint_candidate, const int *hint_kind, int n_hints,
+                                      uint64_t *out_buffer, uint64_t *out_offset, int *n_out, uint64_t *total,
+                                      uint64_t *sel_buffer, uint64_t *sel_reused, int *n_sel) {
+  if (n_traces < 0 || n_hints < 0 || !n_out || !total || !n_sel) return GCB200_INVALID_ARGUMENT;
+  try {
+    std::vector<memplan::Trace> tr;
+    for (int i = 0; i < n_traces; ++i) tr.push_back(memplan::Trace{trace_buffer[i], size_t(trace_size[i])});
+    memplan::InplaceHints hints;
+    for (int i = 0; i < n_hints; ++i)
+      hints[hint_buffer[i]].emplace_back(hint_candidate[i], hint_kind[i] ? memplan::InplaceKind::Free : memplan::InplaceKind::ZeroOffset);
+    std::unordered_map<uint64_t, size_t> off;
+    std::unordered_map<uint64_t, std::vector<uint64_t>> reused;
+    *total = memplan::schedule(tr, size_t(alignment), hot_first != 0, hints, off, reused);
+    int k = 0;
+    for (auto &kv : off) {
+      if (k < *n_out && out_buffer && out_offset) { out_buffer[k] = kv.first; out_offset[k] = kv.second; }
+      ++k;
+    }
+    const bool fits = k <= *n_out;
+    *n_out = k;
+    int m = 0;
+    for (auto &kv : reused)
+      for (uint64_t r : kv.second) {
+        if (m < *n_sel && sel_buffer && sel_reused) { sel_buffer[m] = kv.first; sel_reused[m] = r; }
+        ++m;
+      }
+    const bool fits2 = m <= *n_sel;
+    *n_sel = m;
+    return (fits && fits2) ? GCB200_OK : GCB200_INVALID_ARGUMENT;
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+    return GCB200_INVALID_ARGUMENT;
+  }
 }
 
 GCB_EXPORT int gcb200_plan_arena(const int64_t *bytes, const int *first, const int *last, int n, int64_t align,

@@ -1,4 +1,5 @@
 #include "graph.h"
+#include "memplan.h"
 
 #include <algorithm>
 #include <limits>
@@ -257,31 +258,24 @@ Partition read_partition(const std::string &json) {
 
 // ----------------------------------------------------------------------------- arena planner
 size_t plan_arena(const std::vector<BufferLife> &bufs, size_t align, std::vector<size_t> &offsets) {
+  // Lifetimes -> the allocation / release trace the planner takes (the reference collects the same
+  // trace from alloc and last-use ticks, MergeAllocTickBased.cpp:435-464): at step t first the
+  // buffers born at t are allocated, then those last used at t are released, so a step's inputs
+  // and outputs never share memory.
   offsets.assign(bufs.size(), 0);
-  std::vector<size_t> order(bufs.size());
-  for (size_t i = 0; i < order.size(); ++i) order[i] = i;
-  auto up = [&](size_t v) { return (v + align - 1) / align * align; };
-  std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return bufs[a].bytes > bufs[b].bytes; });
-  std::vector<size_t> placed;
-  size_t total = 0;
-  for (size_t idx : order) {
-    const BufferLife &b = bufs[idx];
-    // memory intervals of already placed buffers whose lifetimes overlap this one
-    std::vector<std::pair<size_t, size_t>> busy;
-    for (size_t j : placed) {
-      const BufferLife &o = bufs[j];
-      if (o.first <= b.last && b.first <= o.last) busy.emplace_back(offsets[j], offsets[j] + up(o.bytes));
-    }
-    std::sort(busy.begin(), busy.end());
-    size_t off = 0;
-    for (auto &iv : busy) {
-      if (off + up(b.bytes) <= iv.first) break;
-      off = std::max(off, iv.second);
-    }
-    offsets[idx] = off;
-    total = std::max(total, off + up(b.bytes));
-    placed.push_back(idx);
+  int last_step = -1;
+  for (const BufferLife &b : bufs) last_step = std::max(last_step, std::max(b.first, b.last));
+  std::vector<memplan::Trace> traces;
+  for (int t = 0; t <= last_step; ++t) {
+    for (size_t i = 0; i < bufs.size(); ++i)
+      if (bufs[i].first == t && bufs[i].bytes > 0) traces.push_back(memplan::Trace{uint64_t(i) + 1, bufs[i].bytes});
+    for (size_t i = 0; i < bufs.size(); ++i)
+      if (std::max(bufs[i].last, bufs[i].first) == t && bufs[i].bytes > 0) traces.push_back(memplan::Trace{uint64_t(i) + 1, 0});
   }
+  std::unordered_map<uint64_t, size_t> out;
+  std::unordered_map<uint64_t, std::vector<uint64_t>> reused;
+  const size_t total = memplan::schedule(traces, align, /*hot_first=*/false, memplan::InplaceHints(), out, reused);
+  for (auto &kv : out) offsets[size_t(kv.first - 1)] = kv.second;
   return total;
 }
 

@@ -189,6 +189,41 @@ class GraphCompiler:
             pass
 
 
+def schedule_memory(traces, alignment=1, hot_first=False, inplace=None):
+    """The static memory planner on a raw trace — the interface of the reference's
+    ``memoryplan::scheduleMemoryAllocations`` (include/gc/Transforms/StaticMemoryPlanning.h:57-62).
+
+    traces: [(buffer id, size)], size 0 releases.  inplace: {buffer: [(candidate, "free" | "zero_offset"), ...]}.
+    Returns (total, {buffer: offset}, {buffer: [reused buffers]})."""
+    l = _bind()
+    U64 = C.c_uint64
+    n = len(traces)
+    tb = (U64 * max(n, 1))(*[t[0] for t in traces])
+    ts = (U64 * max(n, 1))(*[t[1] for t in traces])
+    hb, hc, hk = [], [], []
+    for b, cands in (inplace or {}).items():
+        for c, kind in cands:
+            hb.append(b); hc.append(c); hk.append(1 if kind == "free" else 0)
+    nh = len(hb)
+    a_hb, a_hc, a_hk = (U64 * max(nh, 1))(*hb), (U64 * max(nh, 1))(*hc), (C.c_int * max(nh, 1))(*hk)
+    cap = n + 1
+    ob, oo = (U64 * cap)(), (U64 * cap)()
+    sb, sr = (U64 * (nh + 1))(), (U64 * (nh + 1))()
+    n_out, n_sel, total = C.c_int(cap), C.c_int(nh + 1), U64(0)
+    l.gcb200_schedule_memory.argtypes = [C.POINTER(U64), C.POINTER(U64), C.c_int, U64, C.c_int, C.POINTER(U64), C.POINTER(U64),
+                                         C.POINTER(C.c_int), C.c_int, C.POINTER(U64), C.POINTER(U64), C.POINTER(C.c_int),
+                                         C.POINTER(U64), C.POINTER(U64), C.POINTER(U64), C.POINTER(C.c_int)]
+    st = l.gcb200_schedule_memory(tb, ts, n, alignment, int(hot_first), a_hb, a_hc, a_hk, nh, ob, oo, C.byref(n_out),
+                                  C.byref(total), sb, sr, C.byref(n_sel))
+    if st != 0:
+        raise ValueError("bad planner request: " + _lib.load().gcb200_last_error().decode(errors="replace"))
+    offsets = {int(ob[i]): int(oo[i]) for i in range(n_out.value)}
+    reused: Dict[int, list] = {}
+    for i in range(n_sel.value):
+        reused.setdefault(int(sb[i]), []).append(int(sr[i]))
+    return int(total.value), offsets, reused
+
+
 def plan_arena(sizes, first, last, align=64):
     """Offsets and total size for buffers live over step ranges [first, last]."""
     n = len(sizes)

@@ -155,6 +155,16 @@ int gcb200_execute_on_stream(const struct dnnl_graph_compiler_executable *exe, s
 int gcb200_plan_dump(const struct dnnl_graph_compiler_executable *exe, char *buf, size_t cap, size_t *needed);
 int gcb200_plan_arena(const int64_t *bytes, const int *first, const int *last, int n, int64_t align, int64_t *offsets,
                       int64_t *total);
+/* The planner on a raw trace, with the reference's interface (memoryplan::scheduleMemoryAllocations,
+ * include/gc/Transforms/StaticMemoryPlanning.h:57-62): trace i allocates trace_size[i] elements for buffer
+ * trace_buffer[i], or releases it when the size is 0; hint i says buffer hint_buffer[i] may take over
+ * hint_candidate[i] in place (hint_kind 0: only at its start, 1: anywhere inside; order matters).
+ * Out: (buffer, offset) pairs for every buffer, the total size, and (buffer, reused buffer) pairs.
+ * n_out / n_sel: capacity in, count out.  Needs no device. */
+int gcb200_schedule_memory(const uint64_t *trace_buffer, const uint64_t *trace_size, int n_traces, uint64_t alignment,
+                           int hot_first, const uint64_t *hint_buffer, const uint64_t *hint_candidate,
+                           const int *hint_kind, int n_hints, uint64_t *out_buffer, uint64_t *out_offset, int *n_out,
+                           uint64_t *total, uint64_t *sel_buffer, uint64_t *sel_reused, int *n_sel);
 
 /* ---------------------------------------------------------------------------
  * Split-K bf16 matmul that allocates nothing.  No counterpart in the reference
