@@ -199,6 +199,9 @@ struct dnnl_graph_compiler_executable {
   mutable bool ready = false;
   mutable int device = -1;
   mutable cudaStream_t stream = nullptr;
+  mutable cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host copies that overlap the first / last matmul
+  mutable cudaEvent_t ev_in[4] = {}, ev_out[4] = {};
+  mutable int *host_code = nullptr;                             // pinned: the device error word after a call
   mutable DeviceBuffer arena;
   mutable std::vector<DeviceBuffer> in_stage, out_stage;
   mutable std::vector<char> comp_ready; // per QMATMUL scratch: column sums computed for a cached constant weight
@@ -206,6 +209,13 @@ struct dnnl_graph_compiler_executable {
   explicit dnnl_graph_compiler_executable(const std::string &json) : plan(build_plan(read_partition(json))) {}
   ~dnnl_graph_compiler_executable() {
     if (stream) cudaStreamDestroy(stream);
+    if (copy_in) cudaStreamDestroy(copy_in);
+    if (copy_out) cudaStreamDestroy(copy_out);
+    for (int i = 0; i < 4; ++i) {
+      if (ev_in[i]) cudaEventDestroy(ev_in[i]);
+      if (ev_out[i]) cudaEventDestroy(ev_out[i]);
+    }
+    if (host_code) cudaFreeHost(host_code);
   }
 
   void prepare() const {
@@ -213,6 +223,13 @@ struct dnnl_graph_compiler_executable {
     DeviceState &d = device_state();
     device = d.device;
     GCB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    GCB_CUDA(cudaStreamCreateWithFlags(&copy_in, cudaStreamNonBlocking));
+    GCB_CUDA(cudaStreamCreateWithFlags(&copy_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 4; ++i) {
+      GCB_CUDA(cudaEventCreateWithFlags(&ev_in[i], cudaEventDisableTiming));
+      GCB_CUDA(cudaEventCreateWithFlags(&ev_out[i], cudaEventDisableTiming));
+    }
+    GCB_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&host_code), sizeof(int), cudaHostAllocDefault));
     if (plan.arena_bytes) arena.reserve(plan.arena_bytes);
     in_stage.resize(plan.part.input_ids.size());
     out_stage.resize(plan.part.output_ids.size());
@@ -245,6 +262,28 @@ struct dnnl_graph_compiler_executable {
     if (!t->data && n) throw std::invalid_argument("Tensor " + std::to_string(lt.id) + " has no data");
   }
 
+  // A bf16 tensor-core MatMul whose rows can be computed in independent chunks: used to overlap the
+  // host copy of its A operand (first step) or of its result (last step) with the other chunk's math.
+  // Two chunks of >= 256 rows: each chunk still fills the SMs and re-reads the weights only once more.
+  static constexpr int kRowChunks = 2;
+  bool rows_chunkable(const Step &st) const {
+    const Partition &p = plan.part;
+    if (st.kind != StepKind::MATMUL || st.trans_a) return false;
+    const LogicalTensor &A = p.tensors.at(st.in[0]);
+    if (A.dtype != DType::BF16 || !is_dense(A) || !is_dense(p.tensors.at(st.in[1]))) return false;
+    if (st.M < 512 || st.M % (128 * kRowChunks)) return false;
+    return (st.K % 8) == 0 && (st.N % 8) == 0;
+  }
+  void matmul_rows(const Step &st, const void *a, const void *b, const void *bias, void *out, int64_t r0, int64_t rows,
+                   cudaStream_t s) const {
+    MatmulArgs m;
+    m.A = static_cast<const uint8_t *>(a) + size_t(r0) * size_t(st.K) * 2;
+    m.B = b; m.M = rows; m.N = st.N; m.K = st.K; m.trans_a = 0; m.trans_b = st.trans_b;
+    m.out_kind = OUT_BF16; m.out = static_cast<uint8_t *>(out) + size_t(r0) * size_t(st.N) * 2;
+    m.bias_kind = bias ? BIAS_BF16 : BIAS_NONE; m.bias = bias; m.relu = st.relu;
+    matmul_tc(m, s);
+  }
+
   // own_stream: run on the executable's private stream (the synchronous C API); otherwise on
   // `user_stream`, where a null handle means the legacy default stream, as everywhere in CUDA.
   void execute(dnnl_graph_compiler_tensor *inputs, dnnl_graph_compiler_tensor *outputs, cudaStream_t user_stream,
@@ -255,6 +294,19 @@ struct dnnl_graph_compiler_executable {
     const Partition &p = plan.part;
     const size_t ni = p.input_ids.size(), no = p.output_ids.size();
     std::vector<void *> in_ptr(ni), out_ptr(no), out_host(no, nullptr);
+    // host copies overlapped with the first / last step (synchronous API only)
+    const Step *first = plan.steps.empty() ? nullptr : &plan.steps.front();
+    const Step *last = plan.steps.empty() ? nullptr : &plan.steps.back();
+    long piped_in = -1, piped_out = -1;   // argument index whose copy is chunked
+    const void *piped_in_host = nullptr;
+    if (own_stream && first && rows_chunkable(*first)) {
+      const TensorSlot &sl = plan.slots.at(first->in[0]);
+      if (sl.where == TensorSlot::INPUT && !p.tensors.at(first->in[0]).constant) piped_in = long(sl.index);
+    }
+    if (own_stream && last && rows_chunkable(*last)) {
+      const TensorSlot &sl = plan.slots.at(last->out[0]);
+      if (sl.where == TensorSlot::OUTPUT) piped_out = long(sl.index);
+    }
     for (size_t i = 0; i < ni; ++i) {
       const LogicalTensor &lt = p.tensors.at(p.input_ids[i]);
       dnnl_graph_compiler_tensor *t = find(inputs, ni, i, lt.id);
@@ -262,6 +314,11 @@ struct dnnl_graph_compiler_executable {
       const size_t bytes = span_elems(lt) * dtype_bytes(lt.dtype);
       if (on_device(t->data)) {
         in_ptr[i] = t->data;
+        if (long(i) == piped_in) piped_in = -1;
+      } else if (long(i) == piped_in) {
+        in_stage[i].reserve(bytes);
+        in_ptr[i] = in_stage[i].ptr;
+        piped_in_host = t->data;
       } else {
         DeviceBuffer &b = in_stage[i];
         const bool resident = lt.constant && b.cached_host == t->data && b.bytes >= bytes;
@@ -281,6 +338,7 @@ struct dnnl_graph_compiler_executable {
       const size_t bytes = size_t(lt.numel()) * dtype_bytes(lt.dtype);
       if (on_device(t->data)) {
         out_ptr[i] = t->data;
+        if (long(i) == piped_out) piped_out = -1;
       } else {
         out_stage[i].reserve(bytes);
         out_ptr[i] = out_stage[i].ptr;
@@ -302,18 +360,63 @@ struct dnnl_graph_compiler_executable {
       if (sl.where == TensorSlot::OUTPUT) return out_ptr[sl.index];
       return static_cast<uint8_t *>(arena.ptr) + sl.offset;
     };
-    for (const Step &st : plan.steps) run_step(st, addr, in_ptr, s);
+    // the chunked form goes straight to the tensor-core kernel: its operands must be addressable by TMA
+    auto tc_ok = [&](const Step &st) {
+      return tma_compatible(addr(st.in[0]), st.K, 2) && tma_compatible(addr(st.in[1]), st.trans_b ? st.K : st.N, 2) &&
+             tma_compatible(addr(st.out[0]), st.N, 2);
+    };
+    if (piped_in >= 0 && !tc_ok(*first)) {
+      const LogicalTensor &lt = p.tensors.at(first->in[0]);
+      GCB_CUDA(cudaMemcpyAsync(in_ptr[size_t(piped_in)], piped_in_host, span_elems(lt) * dtype_bytes(lt.dtype),
+                               cudaMemcpyHostToDevice, s));
+      piped_in = -1;
+    }
+    if (piped_out >= 0 && !tc_ok(*last)) piped_out = -1;
+    for (size_t k = 0; k < plan.steps.size(); ++k) {
+      const Step &st = plan.steps[k];
+      const bool chunk_in = (k == 0 && piped_in >= 0), chunk_out = (k + 1 == plan.steps.size() && piped_out >= 0);
+      if (!chunk_in && !chunk_out) {
+        run_step(st, addr, in_ptr, s);
+        continue;
+      }
+      // the step runs as kRowChunks row blocks: block c starts when its rows of A have arrived, and its
+      // rows of the result start their way back to the host while block c + 1 computes
+      const void *a = addr(st.in[0]), *b = addr(st.in[1]);
+      const void *bias = st.has_bias ? addr(st.in[2]) : nullptr;
+      void *out = addr(st.out[0]);
+      const int64_t rows = st.M / kRowChunks;
+      const size_t in_chunk = size_t(rows) * size_t(st.K) * 2, out_chunk = size_t(rows) * size_t(st.N) * 2;
+      if (chunk_in)
+        for (int c = 0; c < kRowChunks; ++c) {
+          GCB_CUDA(cudaMemcpyAsync(static_cast<uint8_t *>(in_ptr[size_t(piped_in)]) + c * in_chunk,
+                                   static_cast<const uint8_t *>(piped_in_host) + c * in_chunk, in_chunk, cudaMemcpyHostToDevice,
+                                   copy_in));
+          GCB_CUDA(cudaEventRecord(ev_in[c], copy_in));
+        }
+      for (int c = 0; c < kRowChunks; ++c) {
+        if (chunk_in) GCB_CUDA(cudaStreamWaitEvent(s, ev_in[c], 0));
+        matmul_rows(st, a, b, bias, out, c * rows, rows, s);
+        if (chunk_out) {
+          GCB_CUDA(cudaEventRecord(ev_out[c], s));
+          GCB_CUDA(cudaStreamWaitEvent(copy_out, ev_out[c], 0));
+          GCB_CUDA(cudaMemcpyAsync(static_cast<uint8_t *>(out_host[size_t(piped_out)]) + c * out_chunk,
+                                   static_cast<const uint8_t *>(out) + c * out_chunk, out_chunk, cudaMemcpyDeviceToHost, copy_out));
+        }
+      }
+    }
     for (size_t i = 0; i < no; ++i)
-      if (out_host[i]) {
+      if (out_host[i] && long(i) != piped_out) {
         const LogicalTensor &lt = p.tensors.at(p.output_ids[i]);
         GCB_CUDA(cudaMemcpyAsync(out_host[i], out_ptr[i], size_t(lt.numel()) * dtype_bytes(lt.dtype), cudaMemcpyDeviceToHost, s));
       }
     bool any_host = false;
     for (void *h : out_host) any_host |= (h != nullptr);
     if (sync || any_host) {
+      // the error word travels behind the results on the same stream: one wait covers both
+      GCB_CUDA(cudaMemcpyAsync(host_code, device_state().d_error, sizeof(int), cudaMemcpyDeviceToHost, s));
       GCB_CUDA(cudaStreamSynchronize(s));
-      int code = 0;
-      GCB_CUDA(cudaMemcpy(&code, device_state().d_error, sizeof(int), cudaMemcpyDeviceToHost));
+      if (piped_out >= 0) GCB_CUDA(cudaStreamSynchronize(copy_out));
+      const int code = *host_code;
       if (code) {
         GCB_CUDA(cudaMemset(device_state().d_error, 0, sizeof(int)));
         throw std::runtime_error("a kernel gave up a bounded wait (code " + std::to_string(code) + ")");

@@ -212,3 +212,31 @@ def test_mlp_chain_full_size_rows_against_oracle():
         mxl, samel = assert_bf16_close(tbits(got), h, W.shape[0], what=f"mlp layer {i}")
         print(f"  layer {i}: max_abs={mxl:.4g} bit-identical={samel:.5f}")
     print(f"mlp chain 512x4096..: max_abs={mx:.4g} bit-identical={same:.5f}")
+
+
+@pytest.mark.parametrize("layers", [1, 3])
+def test_host_buffers_with_overlapped_copies_match_device_buffers(layers):
+    """With host tensors and >= 512 rows the first / last MatMul run as two row blocks so that the host
+    copies overlap the math; every output row must equal the device-tensor run of the same partition
+    (same K order per row; K is short enough here that no block takes a different K split)."""
+    batch, hidden = 1024, [256, 512, 384, 256][:layers + 1]
+    js, in_ids, out_id = partitions.mlp(batch, hidden, "bf16", [True] * layers, "relu")
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(batch, hidden[0], generator=g).bfloat16()
+    Ws = [(torch.randn(hidden[i], hidden[i + 1], generator=g) * 0.1).bfloat16() for i in range(layers)]
+    Bs = [torch.randn(hidden[i + 1], generator=g).bfloat16() for i in range(layers)]
+    exe = api.GraphCompiler().compile(js)
+    out_h = torch.empty(batch, hidden[-1], dtype=torch.bfloat16).pin_memory()
+    out_d = torch.empty(batch, hidden[-1], dtype=torch.bfloat16, device="cuda")
+    exe.execute(dict(zip(in_ids, [X.pin_memory()] + Ws + Bs)), {out_id: out_h})
+    exe.execute(dict(zip(in_ids, [t.cuda() for t in [X] + Ws + Bs])), {out_id: out_d})
+    assert torch.equal(out_h, out_d.cpu())
+    # and a second call with new activations in the same host buffers (staging buffers are reused)
+    X2 = torch.randn(batch, hidden[0], generator=g).bfloat16()
+    exe.execute(dict(zip(in_ids, [X2] + Ws + Bs)), {out_id: out_h})
+    exe.execute(dict(zip(in_ids, [t.cuda() for t in [X2] + Ws + Bs])), {out_id: out_d})
+    assert torch.equal(out_h, out_d.cpu())
+    h = tbits(X2)
+    for W, b in zip(Ws, Bs):
+        h, acc = oracle.linear_bf16(h, tbits(W), tbits(b), relu=True, return_acc=True)
+    assert_bf16_close(tbits(out_h), h, max(hidden), what="overlapped host path", pre=acc, floor_div=1.0 if layers > 1 else 16.0)
