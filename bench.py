@@ -173,7 +173,7 @@ def cpu_onednn_class(rows=BATCH):
 def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "auto"):
     """Time one kernel-level case with device-resident inputs (CUDA events on the launching stream).
 
-    spec: gemm:M:N:K | decode | int8:M:N:K | attention:B:H:S:D:causal(0|1) | cfg1
+    spec: gemm:M:N:K | decode | int8:M:N:K | attention:B:H:S:D:causal(0|1) | cfg1 | llama2
     Returns a dict with ms, value/unit, the roofline bound and fraction against the measured peak."""
     import math
 
@@ -274,7 +274,7 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "aut
          "l2": "flushed between launches" if flush is not None else "working set larger than L2"}
     if graph_us is not None:
         r["us_per_launch_graph_replay"] = graph_us
-    if kind == "decode":
+    if kind in ("decode", "llama2"):
         r["roofline"] = {"bound": "hbm", "achieved": bytes_ / ms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": bytes_ / ms / 1e6 / peaks["hbm"]}
     elif kind == "int8":

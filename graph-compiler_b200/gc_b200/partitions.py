@@ -99,3 +99,61 @@ def sdpa(batch: int, heads: int, seq: int, dim: int, scale: float, causal: bool)
     op = {"kind": "SDPA", "attrs": {"scale": {"type": "f32", "value": scale}, "causal": {"type": "bool", "value": int(causal)}},
           "inputs": [_t(0, "bf16", sh), _t(1, "bf16", sh), _t(2, "bf16", sh)], "outputs": [_t(3, "bf16", sh)]}
     return _envelope([op], [0, 1, 2], [3]), [0, 1, 2], 3
+
+
+def llama2_mlp(batch: int = 1, seq: int = 32, hidden: int = 4096, inter: int = 11008, constant_weights: bool = False):
+    """The llama2 decoder MLP block of the reference's tests
+    (test/mlir/test/gc/Dialect/OneDNNGraph/onednn-graph-llama2.mlir:5-45; linalg form
+    test/benchgc/cases/llama2.mlir): attention-output projection + residual, RMSNorm, SiLU-gated MLP with
+    three transpose_b MatMuls, residual, second RMSNorm.  Only the reference's own op kinds are used.
+
+    Returns (json, {name: id} of the ten arguments in the reference's order, [id of the normed output, id of the residual output]).
+    Arguments: x [B,S,H], wo [H,H], resid [B,S,H], eps1 [1] f32 (unused by the graph, kept for the signature),
+    g1 [H], w_gate [I,H], w_up [I,H], w_down [H,I], eps [1] f32, g2 [H]."""
+    B, S, H, I = batch, seq, hidden, inter
+    bf, f32 = "bf16", "f32"
+    act, act32, row = [B, S, H], [B, S, H], [B, S, 1]
+    ids = {"x": 0, "wo": 1, "resid": 2, "eps1": 3, "g1": 4, "w_gate": 5, "w_up": 6, "w_down": 7, "eps": 8, "g2": 9}
+    nxt = [10]
+
+    def new():
+        nxt[0] += 1
+        return nxt[0] - 1
+
+    g = []
+    cw = constant_weights
+
+    def op(kind, ins, out, attrs=None):
+        d = {"kind": kind, "inputs": ins, "outputs": [out]}
+        if attrs:
+            d["attrs"] = attrs
+        g.append(d)
+        return out["id"]
+
+    tb = {"transpose_b": {"type": "bool", "value": 1}}
+    t5 = op("MatMul", [_t(ids["x"], bf, act), _t(ids["wo"], bf, [H, H], cw)], _t(new(), bf, act), tb)
+    t7 = op("Add", [_t(ids["resid"], bf, act), _t(t5, bf, act)], _t(new(), bf, act))
+
+    def rmsnorm(src, gamma):
+        c = op("Typecast", [_t(src, bf, act)], _t(new(), f32, act32))
+        sq = op("Pow", [_t(c, f32, act32)], _t(new(), f32, act32), {"beta": {"type": "f32", "value": 2.0}})
+        mean = op("ReduceMean", [_t(sq, f32, act32)], _t(new(), f32, row),
+                  {"axes": {"type": "s64[]", "value": [-1]}, "keep_dims": {"type": "bool", "value": 1}})
+        pe = op("Add", [_t(mean, f32, row), _t(ids["eps"], f32, [1])], _t(new(), f32, row))
+        rs = op("Pow", [_t(pe, f32, row)], _t(new(), f32, row), {"beta": {"type": "f32", "value": -0.5}})
+        sc = op("Multiply", [_t(c, f32, act32), _t(rs, f32, row)], _t(new(), f32, act32))
+        back = op("Typecast", [_t(sc, f32, act32)], _t(new(), bf, act))
+        return op("Multiply", [_t(gamma, bf, [H], cw), _t(back, bf, act)], _t(new(), bf, act))
+
+    t27 = rmsnorm(t7, ids["g1"])
+    wide = [B, S, I]
+    t30 = op("MatMul", [_t(t27, bf, act), _t(ids["w_gate"], bf, [I, H], cw)], _t(new(), bf, wide), tb)
+    t31 = op("Sigmoid", [_t(t30, bf, wide)], _t(new(), bf, wide))
+    t32 = op("Multiply", [_t(t31, bf, wide), _t(t30, bf, wide)], _t(new(), bf, wide))
+    t35 = op("MatMul", [_t(t27, bf, act), _t(ids["w_up"], bf, [I, H], cw)], _t(new(), bf, wide), tb)
+    t36 = op("Multiply", [_t(t32, bf, wide), _t(t35, bf, wide)], _t(new(), bf, wide))
+    t39 = op("MatMul", [_t(t36, bf, wide), _t(ids["w_down"], bf, [H, I], cw)], _t(new(), bf, act), tb)
+    t41 = op("Add", [_t(t7, bf, act), _t(t39, bf, act)], _t(new(), bf, act))
+    t61 = rmsnorm(t41, ids["g2"])
+    used = [ids[k] for k in ("x", "wo", "resid", "g1", "w_gate", "w_up", "w_down", "eps", "g2")]
+    return _envelope(g, used, [t61, t41]), ids, [t61, t41]

@@ -240,3 +240,54 @@ def test_host_buffers_with_overlapped_copies_match_device_buffers(layers):
     for W, b in zip(Ws, Bs):
         h, acc = oracle.linear_bf16(h, tbits(W), tbits(b), relu=True, return_acc=True)
     assert_bf16_close(tbits(out_h), h, max(hidden), what="overlapped host path", pre=acc, floor_div=1.0 if layers > 1 else 16.0)
+
+
+def _llama2_reference(t, eps):
+    """The block of onednn-graph-llama2.mlir:5-45 on the host: bf16 ops are evaluated in f32 and rounded
+    after every op (Pipeline.cpp:81-90), MatMul accumulates in f32 and rounds once, f32 ops stay f32."""
+    r = lambda v: v.to(torch.bfloat16).to(torch.float32)                   # one bf16 rounding
+    f = lambda v: v.to(torch.float32)
+    mm = lambda a, w: r(f(a) @ f(w).t())
+
+    def rmsnorm(h, gamma):
+        c = f(h)
+        rs = torch.pow(torch.pow(c, 2.0).mean(-1, keepdim=True) + eps, -0.5)
+        return r(f(gamma) * r(c * rs))
+
+    t7 = r(f(t["resid"]) + mm(t["x"], t["wo"]))
+    t27 = rmsnorm(t7, t["g1"])
+    t30 = mm(t27, t["w_gate"])
+    t32 = r(r(torch.sigmoid(t30)) * t30)
+    t36 = r(t32 * mm(t27, t["w_up"]))
+    t39 = mm(t36, t["w_down"])
+    t41 = r(t7 + t39)
+    return rmsnorm(t41, t["g2"]), t41, t7.abs() + t39.abs()
+
+
+@pytest.mark.parametrize("dims", [(1, 32, 512, 1024), (1, 32, 4096, 11008), (2, 40, 256, 384)])
+def test_llama2_mlp_partition(dims):
+    """RMSNorm + SiLU-gated MLP with three transpose_b MatMuls, all eleven reference op kinds but ReLU/Sub/Div."""
+    B, S, H, I = dims
+    js, ids, outs = partitions.llama2_mlp(B, S, H, I)
+    g = torch.Generator().manual_seed(11)
+    bf = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).bfloat16()
+    t = {"x": bf(B, S, H), "wo": bf(H, H, scale=H ** -0.5), "resid": bf(B, S, H), "g1": bf(H) * 0.1 + 1, "w_gate": bf(I, H, scale=H ** -0.5),
+         "w_up": bf(I, H, scale=H ** -0.5), "w_down": bf(H, I, scale=I ** -0.5), "g2": bf(H) * 0.1 + 1}
+    t["g1"], t["g2"] = t["g1"].bfloat16(), t["g2"].bfloat16()
+    eps = torch.tensor([1e-5], dtype=torch.float32)
+    want_norm, want_res, add_operands = _llama2_reference(t, eps)
+    exe = api.GraphCompiler().compile(js)
+    ins = {ids[k]: v.cuda() for k, v in t.items()}
+    ins[ids["eps"]] = eps.cuda()
+    o_norm = torch.empty(B, S, H, dtype=torch.bfloat16, device="cuda")
+    o_res = torch.empty(B, S, H, dtype=torch.bfloat16, device="cuda")
+    exe.execute(ins, {outs[0]: o_norm, outs[1]: o_res})
+    # The residual is bf16(t7 + bf16(matmul)): a 1-ulp flip of either rounded operand (any change of f32
+    # summation order causes some) reaches the sum as up to two ulps — the double-rounding allowance of
+    # assert_bf16_close with the operands' magnitudes as `pre`.  RMSNorm is scale-free: the normed output
+    # inherits those two ulps and adds one per rounding of its two bf16 multiplies — four ulps of at most
+    # 2^-7 relative each (pre = 3 |want|).
+    for name, got, want, pre in (("residual", o_res, want_res, add_operands), ("normed", o_norm, want_norm, 3 * want_norm.abs())):
+        mx, same = assert_bf16_close(tbits(got), tbits(want.bfloat16()), max(H, I), what=f"llama2 {name} {dims}", floor_div=1.0,
+                                     pre=pre.numpy())
+        print(f"llama2 {dims} {name}: max_abs={mx:.4g} bit-identical={same:.5f}")
