@@ -222,6 +222,22 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "aut
         work, unit = 4.0 * B_ * H * S * S * D * (0.5 if causal else 1.0), "TFLOPS"
         bytes_ = 4 * B_ * H * S * D * 2
         l2_flush = bytes_ < 256e6
+    elif kind == "llama2":
+        # the llama2 decoder MLP block of the reference's tests (onednn-graph-llama2.mlir:5-45), 1 x 32 tokens:
+        # 25 steps, HBM-bound on its 302 MB of weights
+        from gc_b200 import api, partitions
+        Bq, S, H, I = 1, 32, 4096, 11008
+        js, ids, outs = partitions.llama2_mlp(Bq, S, H, I)
+        exe = api.GraphCompiler().compile(js)
+        t = {"x": u((Bq, S, H)), "wo": u((H, H)) * 0.02, "resid": u((Bq, S, H)), "g1": u((H,)), "w_gate": u((I, H)) * 0.02,
+             "w_up": u((I, H)) * 0.02, "w_down": u((H, I)) * 0.02, "g2": u((H,))}
+        ins = {ids[k]: v.bfloat16() for k, v in t.items()}
+        ins[ids["eps"]] = torch.full((1,), 1e-5, device=dev)
+        o = {outs[0]: torch.empty(Bq, S, H, dtype=torch.bfloat16, device=dev), outs[1]: torch.empty(Bq, S, H, dtype=torch.bfloat16, device=dev)}
+        fn = lambda: exe.execute_on_stream(ins, o)
+        work, unit = 2.0 * S * (H * H + 3 * H * I), "TFLOPS"
+        bytes_ = 2 * (H * H + 3 * H * I)
+        l2_flush = False
     else:
         raise ValueError(spec)
     if flush_mode != "auto":
