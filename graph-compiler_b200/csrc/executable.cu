@@ -138,6 +138,41 @@ __global__ void reduce_kernel(ReduceParams p, const void *a, void *o) {
   }
 }
 
+// Long reductions (e.g. the 4096-wide mean of an RMSNorm): one block per output element.  Thread t sums
+// elements t, t + 256, ... in ascending order, then the 256 partial sums are combined in a fixed tree,
+// so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) reduce_block_kernel(ReduceParams p, const void *a, void *o) {
+  __shared__ float part[256];
+  for (long long i = blockIdx.x; i < p.out_total; i += gridDim.x) {
+    long long r = i, base = 0;
+    for (int d = p.nk - 1; d >= 0; --d) {
+      base += (r % p.kdims[d]) * p.kstr[d];
+      r /= p.kdims[d];
+    }
+    float s = 0.f;
+    for (long long j = threadIdx.x; j < p.red_total; j += 256) {
+      long long q = j, off = base;
+      for (int d = p.nr - 1; d >= 0; --d) {
+        off += (q % p.rdims[d]) * p.rstr[d];
+        q /= p.rdims[d];
+      }
+      s = __fadd_rn(s, ew_load(a, off, p.dt_a));
+    }
+    part[threadIdx.x] = s;
+    __syncthreads();
+    for (int w = 128; w > 0; w >>= 1) {
+      if (int(threadIdx.x) < w) part[threadIdx.x] = __fadd_rn(part[threadIdx.x], part[threadIdx.x + w]);
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+      float t = part[0];
+      if (p.mean) t = __fdiv_rn(t, float(p.red_total));
+      ew_store(o, i, p.dt_o, t);
+    }
+    __syncthreads();
+  }
+}
+
 static int ew_dtype(DType t) {
   switch (t) {
   case DType::F32: return 0;
@@ -537,9 +572,14 @@ struct dnnl_graph_compiler_executable {
       r.mean = st.mean ? 1 : 0;
       r.dt_a = ew_dtype(A.dtype);
       r.dt_o = ew_dtype(O.dtype);
-      const int threads = 128;
-      const int blocks = int(std::min<long long>((r.out_total + threads - 1) / threads, 148LL * 16));
-      reduce_kernel<<<std::max(blocks, 1), threads, 0, s>>>(r, addr(st.in[0]), addr(st.out[0]));
+      if (r.red_total >= 512 && r.out_total > 0) {
+        const int blocks = int(std::min<long long>(r.out_total, 148LL * 8));
+        reduce_block_kernel<<<blocks, 256, 0, s>>>(r, addr(st.in[0]), addr(st.out[0]));
+      } else {
+        const int threads = 128;
+        const int blocks = int(std::min<long long>((r.out_total + threads - 1) / threads, 148LL * 16));
+        reduce_kernel<<<std::max(blocks, 1), threads, 0, s>>>(r, addr(st.in[0]), addr(st.out[0]));
+      }
       GCB_CUDA(cudaGetLastError());
       count_launch();
       break;

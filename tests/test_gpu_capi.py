@@ -116,6 +116,13 @@ def test_ops_pow_relu_sigmoid_typecast_reduce():
         if mean:
             want = want / np.float32(64)
         np.testing.assert_array_equal(o[:, 0, :], want)
+    # long reductions run one block per output element; integer-valued data keeps every order exact
+    big = (np.arange(6 * 5000, dtype=np.float32).reshape(6, 5000) % 97) - 48
+    for kind, want in (("ReduceSum", big.sum(1)), ("ReduceMean", big.sum(1) / np.float32(5000))):
+        o = np.empty((6,), np.float32)
+        _run([{"kind": kind, "attrs": {"axes": {"type": "s64[]", "value": [-1]}},
+               "inputs": [_t(0, "f32", [6, 5000])], "outputs": [_t(1, "f32", [6])]}], {0: big}, {1: o})
+        np.testing.assert_array_equal(o, want.astype(np.float32))
 
 
 def test_add_relu_bf16_broadcast_rounds_per_op():
