@@ -206,7 +206,8 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
 }
 }
 
-// TMA-store form of the row-major epilogue (bf16 with optional bias / ReLU, or raw f32 / s32 planes).
+// TMA-store form of the row-major epilogue (bf16 with optional bias / ReLU, int8 dequantisation to f32, or
+// raw f32 / s32 planes).
 // Each thread owns one accumulator row: TMEM -> registers -> rounding and post-ops on packed pairs ->
 // 16-byte chunks into a swizzled 32 x 128-byte staging slab -> one cp.async.bulk.tensor store per slab
 // issued by lane 0.  Two staging slabs per warp alternate, so the copy engine drains one while the
@@ -240,10 +241,37 @@ __device__ __forceinline__ void gemm_epilogue_tile_tma(const GemmParams &p, uint
       const uint32_t b0 = c < p.out_cols ? b[c] : 0u, b1 = c + 1 < p.out_cols ? b[c + 1] : 0u;
       bias2 = b0 | (b1 << 16);
     }
+    // int8 dequantisation: this lane holds scale / bias / compensation of column col0 + lane
+    float q_scale = 1.f, q_bias = 0.f;
+    int32_t q_comp = 0;
+    if (p.out_kind == OUT_DEQUANT_F32) {
+      const int c = col0 + lane;
+      if (c < p.out_cols) {
+        q_scale = p.scale[c];
+        if (p.bias_kind == BIAS_F32) q_bias = reinterpret_cast<const float *>(p.bias)[c];
+        if (p.comp) q_comp = p.comp[c];
+      }
+    }
     tmem_wait_ld();
     __syncwarp();
     uint8_t *slab = stg + buf * 4096u;
-    if (two_byte) {
+    if (p.out_kind == OUT_DEQUANT_F32) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 4 * c + e;
+          const float sc = __shfl_sync(0xFFFFFFFFu, q_scale, j), bi = __shfl_sync(0xFFFFFFFFu, q_bias, j);
+          const int32_t cp = __shfl_sync(0xFFFFFFFFu, q_comp, j);
+          float f = __fmul_rn(float(int32_t(v[j]) - cp), sc);
+          if (p.bias_kind == BIAS_F32) f = __fadd_rn(f, bi);
+          if (p.relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
+          w[e] = __float_as_uint(f);
+        }
+        *reinterpret_cast<uint4 *>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else if (two_byte) {
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t w[4];

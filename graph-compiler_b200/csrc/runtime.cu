@@ -386,8 +386,9 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   // copy engine can address the output (16-byte aligned base and row pitch)
   if (!pair && !cfg.swapped && a.n_peers == 0 && p.acc_dump == nullptr) {
     const int esz = p.out_kind == OUT_BF16 ? 2 : 4;
-    const bool plain = p.out_kind == OUT_BF16 ? (p.bias_kind == BIAS_NONE || p.bias_kind == BIAS_BF16)
-                                              : ((p.out_kind == OUT_F32 || p.out_kind == OUT_S32) && p.bias_kind == BIAS_NONE && !p.relu);
+    const bool plain = p.out_kind == OUT_BF16          ? (p.bias_kind == BIAS_NONE || p.bias_kind == BIAS_BF16)
+                       : p.out_kind == OUT_DEQUANT_F32 ? (p.bias_kind == BIAS_NONE || p.bias_kind == BIAS_F32)
+                                                       : ((p.out_kind == OUT_F32 || p.out_kind == OUT_S32) && p.bias_kind == BIAS_NONE && !p.relu);
     if (plain && tma_compatible(p.out, p.ld_out, esz) && (!split || (size_t(p.split_stride) * esz) % 16 == 0)) {
       const ElemType ct = p.out_kind == OUT_BF16 ? ElemType::BF16 : (p.out_kind == OUT_S32 ? ElemType::S32 : ElemType::F32);
       p.tmC = make_tmap_3d(ct, p.out, uint64_t(a.N), uint64_t(a.M), uint64_t(std::max(1, p.splits)), uint64_t(p.ld_out) * esz,
