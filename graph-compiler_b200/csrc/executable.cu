@@ -7,6 +7,7 @@
 // argument marshalling, status mapping) and lib/gc/ExecutionEngine/Driver/
 // Driver.cpp:60-89 (the JIT engine this replaces).
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -237,6 +238,16 @@ struct dnnl_graph_compiler_executable {
   mutable cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host copies that overlap the first / last matmul
   mutable cudaEvent_t ev_in[4] = {}, ev_out[4] = {};
   mutable int *host_code = nullptr;                             // pinned: the device error word after a call
+  // Replay of the launch list as a CUDA graph when a call repeats an earlier call's device addresses:
+  // the first call runs eagerly (it also sizes the workspaces), the second is captured, later ones replay.
+  struct GraphEntry {
+    std::vector<const void *> key;
+    cudaGraphExec_t exec = nullptr;
+    unsigned long long ws_generation = 0, kernels = 0, last_use = 0;
+    bool unusable = false;
+  };
+  mutable std::vector<GraphEntry> graphs;
+  mutable unsigned long long graph_clock = 0;
   mutable DeviceBuffer arena;
   mutable std::vector<DeviceBuffer> in_stage, out_stage;
   mutable std::vector<char> comp_ready; // per QMATMUL scratch: column sums computed for a cached constant weight
@@ -251,6 +262,8 @@ struct dnnl_graph_compiler_executable {
       if (ev_out[i]) cudaEventDestroy(ev_out[i]);
     }
     if (host_code) cudaFreeHost(host_code);
+    for (GraphEntry &g : graphs)
+      if (g.exec) cudaGraphExecDestroy(g.exec);
   }
 
   void prepare() const {
@@ -407,7 +420,75 @@ struct dnnl_graph_compiler_executable {
       piped_in = -1;
     }
     if (piped_out >= 0 && !tc_ok(*last)) piped_out = -1;
-    for (size_t k = 0; k < plan.steps.size(); ++k) {
+    // ---- every tensor in device memory: the launch list does not depend on anything but the addresses
+    bool all_dev = true;
+    for (size_t i = 0; i < ni; ++i) all_dev &= (in_ptr[i] != in_stage[i].ptr || in_stage[i].ptr == nullptr);
+    for (size_t i = 0; i < no; ++i) all_dev &= (out_host[i] == nullptr);
+    static const bool graphs_on = [] { const char *e = std::getenv("GC_B200_GRAPHS"); return !(e && e[0] == '0'); }();
+    bool replayed = false;
+    if (all_dev && graphs_on && plan.steps.size() > 1) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(s, &cs) != cudaSuccess) { cudaGetLastError(); cs = cudaStreamCaptureStatusActive; }
+      if (cs == cudaStreamCaptureStatusNone) {
+        std::vector<const void *> key(in_ptr.begin(), in_ptr.end());
+        key.insert(key.end(), out_ptr.begin(), out_ptr.end());
+        GraphEntry *ge = nullptr;
+        for (GraphEntry &g : graphs)
+          if (g.key == key) ge = &g;
+        const unsigned long long gen = device_state().workspace_generation;
+        if (ge && ge->exec && ge->ws_generation != gen) {   // a workspace moved: the captured addresses are stale
+          cudaGraphExecDestroy(ge->exec);
+          ge->exec = nullptr;
+        }
+        if (!ge) {
+          // first sight of these addresses: remember them, run eagerly below
+          if (graphs.size() >= 4) {
+            size_t victim = 0;
+            for (size_t i = 1; i < graphs.size(); ++i)
+              if (graphs[i].last_use < graphs[victim].last_use) victim = i;
+            if (graphs[victim].exec) cudaGraphExecDestroy(graphs[victim].exec);
+            graphs.erase(graphs.begin() + long(victim));
+          }
+          graphs.push_back(GraphEntry{});
+          graphs.back().key = key;
+          graphs.back().last_use = ++graph_clock;
+        } else if (!ge->unusable) {
+          ge->last_use = ++graph_clock;
+          if (!ge->exec) {
+            const unsigned long long l0 = launch_count();
+            cudaGraph_t g = nullptr;
+            bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+            if (ok) {
+              try {
+                for (const Step &st : plan.steps) run_step(st, addr, in_ptr, s);
+              } catch (...) {
+                ok = false;
+              }
+              if (cudaStreamEndCapture(s, &g) != cudaSuccess || !g) ok = false;
+            }
+            if (ok && cudaGraphInstantiate(&ge->exec, g, 0) != cudaSuccess) ok = false;
+            if (g) cudaGraphDestroy(g);
+            if (!ok) {
+              cudaGetLastError();
+              if (ge->exec) cudaGraphExecDestroy(ge->exec);
+              ge->exec = nullptr;
+              ge->unusable = true;   // fall back to eager launches for these addresses
+              count_launch(-int(launch_count() - l0));
+            } else {
+              ge->kernels = launch_count() - l0;
+              ge->ws_generation = gen;
+              count_launch(-int(ge->kernels));   // counted when launched, below
+            }
+          }
+          if (ge->exec) {
+            GCB_CUDA(cudaGraphLaunch(ge->exec, s));
+            count_launch(int(ge->kernels));
+            replayed = true;
+          }
+        }
+      }
+    }
+    for (size_t k = 0; k < plan.steps.size() && !replayed; ++k) {
       const Step &st = plan.steps[k];
       const bool chunk_in = (k == 0 && piped_in >= 0), chunk_out = (k + 1 == plan.steps.size() && piped_out >= 0);
       if (!chunk_in && !chunk_out) {

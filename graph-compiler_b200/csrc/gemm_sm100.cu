@@ -93,6 +93,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&bars->tmem_base);
+  // Everything above touched only shared and tensor memory and may overlap the tail of the kernel
+  // ahead in the stream; from here on operands are read and results written.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------------ TMA producers
@@ -259,8 +263,17 @@ cudaError_t launch_gemm_kernel(const CUtensorMap &tmA, const CUtensorMap &tmB, c
     if (e != cudaSuccess) return e;
     configured[dev & 63] = true;
   }
-  kfn<<<grid, kThreads, smem, stream>>>(tmA, tmB, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, p);
 }
 
 template cudaError_t launch_gemm_kernel<0, false>(const CUtensorMap &, const CUtensorMap &, const GemmParams &, int,

@@ -51,6 +51,7 @@ void *DeviceState::ensure_workspace(size_t bytes) {
   size_t want = std::max(bytes, size_t(64) << 20);
   GCB_CUDA(cudaMalloc(&workspace, want));
   workspace_bytes = want;
+  ++workspace_generation;
   return workspace;
 }
 

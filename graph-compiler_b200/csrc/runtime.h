@@ -32,6 +32,7 @@ struct DeviceState {
   int *d_error = nullptr;          // device word written by kernels on a bounded-wait time-out
   void *workspace = nullptr;       // split-K partial planes, column sums
   size_t workspace_bytes = 0;
+  unsigned long long workspace_generation = 0;   // bumped whenever the workspace moves (captured graphs hold its address)
   void *ensure_workspace(size_t bytes); // grows (synchronising) when needed
 };
 DeviceState &device_state();       // throws CudaError when no usable device / driver

@@ -324,6 +324,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
   return r;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute
+// may begin (its CTAs scheduled, its prologue run) before the kernel ahead of it in the stream has
+// finished; pdl_wait() blocks until that kernel has completed and its writes are visible, so every
+// global-memory access of the dependent kernel must come after it.  pdl_launch_dependents() lets the
+// NEXT kernel in the stream be scheduled as soon as every CTA of this grid has called it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // cvt.rn.bf16x2 returns 0x7FFF for a NaN input; the reference conversion returns 0x7FC0
 // (BrgemmInterface.h:83-92).  Patch the (rare) NaN halves of a packed pair.
 __device__ __forceinline__ uint32_t bf16x2_fix_nan(uint32_t w) {

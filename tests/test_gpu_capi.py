@@ -298,3 +298,36 @@ def test_llama2_mlp_partition(dims):
         mx, same = assert_bf16_close(tbits(got), tbits(want.bfloat16()), max(H, I), what=f"llama2 {name} {dims}", floor_div=1.0,
                                      pre=pre.numpy())
         print(f"llama2 {dims} {name}: max_abs={mx:.4g} bit-identical={same:.5f}")
+
+
+def test_repeated_device_calls_replay_a_graph_with_identical_results():
+    """From the third call with the same device addresses the launch list is replayed as a CUDA graph; results
+    must equal those of an eager run (a first call on fresh addresses), and the launch counter keeps counting."""
+    from gc_b200 import lib
+
+    batch, hidden = 256, [256, 512, 256, 128]
+    js, in_ids, out_id = partitions.mlp(batch, hidden, "bf16", [True] * 3, "relu")
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(batch, hidden[0], generator=g).bfloat16().cuda()
+    Ws = [(torch.randn(hidden[i], hidden[i + 1], generator=g) * 0.1).bfloat16().cuda() for i in range(3)]
+    Bs = [torch.randn(hidden[i + 1], generator=g).bfloat16().cuda() for i in range(3)]
+    out = torch.empty(batch, hidden[-1], dtype=torch.bfloat16, device="cuda")
+    exe = api.GraphCompiler().compile(js)
+    per_call = []
+    for it in range(5):
+        X.copy_(torch.randn(batch, hidden[0], generator=g).bfloat16())
+        l0 = lib.launch_count()
+        exe.execute(dict(zip(in_ids, [X] + Ws + Bs)), {out_id: out})
+        per_call.append(lib.launch_count() - l0)
+        fresh_out = torch.empty_like(out)
+        exe.execute(dict(zip(in_ids, [X.clone()] + Ws + Bs)), {out_id: fresh_out})   # new address: eager
+        assert torch.equal(out, fresh_out), it
+    assert len(set(per_call)) == 1 and per_call[0] == 3, per_call
+    # asynchronous form on the caller's stream
+    for it in range(4):
+        X.copy_(torch.randn(batch, hidden[0], generator=g).bfloat16())
+        exe.execute_on_stream(dict(zip(in_ids, [X] + Ws + Bs)), {out_id: out})
+        torch.cuda.synchronize()
+        fresh_out = torch.empty_like(out)
+        exe.execute(dict(zip(in_ids, [X.clone()] + Ws + Bs)), {out_id: fresh_out})
+        assert torch.equal(out, fresh_out), it
