@@ -478,6 +478,32 @@ __global__ void reduce_planes_kernel(const void *parts, int nparts, long long pl
   }
 }
 
+// The common case, f32 planes -> bf16 (+bias, ReLU), four columns per thread with 16-byte loads.  Same
+// arithmetic as the scalar kernel: planes added in split order, one rounding, bias in f32, second rounding.
+__global__ void __launch_bounds__(256)
+reduce_planes_bf16x4_kernel(const float4 *parts, int nparts, long long plane4, uint2 *out, long long total4, int n4,
+                            const uint2 *bias, int relu) {
+  pdl_launch_dependents();
+  pdl_wait();   // the planes come from the kernel ahead in the stream
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    float4 s = parts[i];
+    for (int k = 1; k < nparts; ++k) {
+      const float4 t = parts[(long long)k * plane4 + i];
+      s.x = __fadd_rn(s.x, t.x); s.y = __fadd_rn(s.y, t.y); s.z = __fadd_rn(s.z, t.z); s.w = __fadd_rn(s.w, t.w);
+    }
+    uint32_t lo = pack_bf16x2_rn(s.x, s.y), hi = pack_bf16x2_rn(s.z, s.w);
+    if (bias) {
+      const uint2 b = bias[int(i % n4)];
+      lo = pack_bf16x2_rn(__fadd_rn(__uint_as_float(lo << 16), __uint_as_float(b.x << 16)),
+                          __fadd_rn(__uint_as_float(lo & 0xFFFF0000u), __uint_as_float(b.x & 0xFFFF0000u)));
+      hi = pack_bf16x2_rn(__fadd_rn(__uint_as_float(hi << 16), __uint_as_float(b.y << 16)),
+                          __fadd_rn(__uint_as_float(hi & 0xFFFF0000u), __uint_as_float(b.y & 0xFFFF0000u)));
+    }
+    if (relu) { lo = bf16x2_relu(lo); hi = bf16x2_relu(hi); }
+    out[i] = make_uint2(bf16x2_fix_nan(lo), bf16x2_fix_nan(hi));
+  }
+}
+
 void reduce_planes(const void *parts, int nparts, int64_t plane, void *out, int64_t M, int64_t N, int out_kind,
                    int bias_kind, const void *bias, const float *scale, const int32_t *comp, int32_t *acc_dump,
                    int relu, cudaStream_t stream) {
@@ -486,6 +512,26 @@ void reduce_planes(const void *parts, int nparts, int64_t plane, void *out, int6
   const int threads = 256;
   const int blocks = int(std::min<long long>((total + threads - 1) / threads, (long long)dev.sm_count * 8));
   const bool is_int = (out_kind == OUT_S32 || out_kind == OUT_DEQUANT_F32);
+  auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) & (a - 1)) == 0; };
+  if (!is_int && out_kind == OUT_BF16 && (bias_kind == BIAS_NONE || bias_kind == BIAS_BF16) && N % 4 == 0 && plane % 4 == 0 &&
+      al(parts, 16) && al(out, 8) && (bias_kind == BIAS_NONE || al(bias, 8)) && N / 4 < (1 << 30)) {
+    const long long total4 = total / 4;
+    const int blocks4 = int(std::min<long long>((total4 + threads - 1) / threads, (long long)dev.sm_count * 8));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(std::max(blocks4, 1)));
+    cfg.blockDim = dim3(threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    GCB_CUDA(cudaLaunchKernelEx(&cfg, reduce_planes_bf16x4_kernel, reinterpret_cast<const float4 *>(parts), nparts,
+                                (long long)(plane / 4), reinterpret_cast<uint2 *>(out), total4, int(N / 4),
+                                bias_kind == BIAS_BF16 ? reinterpret_cast<const uint2 *>(bias) : nullptr, relu));
+    count_launch();
+    return;
+  }
   if (is_int)
     reduce_planes_kernel<true><<<blocks, threads, 0, stream>>>(parts, nparts, plane, out, M, N, out_kind, bias_kind,
                                                               bias, scale, comp, acc_dump, relu);
