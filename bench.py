@@ -302,8 +302,8 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "aut
     return r
 
 
-SWEEP = ["cfg1", "int8:1024:4096:4096", "attention:16:32:2048:128:0", "attention:16:32:2048:128:1", "gemm:1024:1024:1024",
-         "gemm:2048:2048:2048", "gemm:4096:4096:4096", "gemm:8192:8192:8192", "gemm:16384:16384:16384", "decode"]
+SWEEP = ["cfg1", "int8:1024:4096:4096", "decode", "attention:16:32:2048:128:0", "attention:16:32:2048:128:1", "gemm:1024:1024:1024",
+         "gemm:2048:2048:2048", "gemm:4096:4096:4096", "gemm:8192:8192:8192", "gemm:16384:16384:16384"]
 
 
 # --------------------------------------------------------------------------------------- GPU arm
