@@ -43,7 +43,30 @@ struct EwParams {
   int fn;                     // binary: 0 add 1 sub 2 mul 3 div; unary: 0 relu 1 sigmoid 2 pow 3 cast
   float beta;
   int dt_a, dt_b, dt_o;       // 0 f32, 1 bf16, 2 f16
+  // how an operand's offset follows from the flat output index i without walking the dims:
+  // 0 general (walk), 1 same layout (i), 2 one value (0), 3 a row vector broadcast over rows (i % c),
+  // 4 one value per row (i / c), c = the innermost output dim
+  int mode_a, mode_b;
+  unsigned inner;
 };
+
+__device__ __forceinline__ long long ew_offset(const EwParams &p, long long i, int mode, const long long *stride) {
+  switch (mode) {
+  case 1: return i;
+  case 2: return 0;
+  case 3: return (long long)(unsigned(i) % p.inner);
+  case 4: return (long long)(unsigned(i) / p.inner);
+  default: {
+    long long r = i, o = 0;
+    for (int d = p.rank - 1; d >= 0; --d) {
+      const long long c = r % p.dims[d];
+      r /= p.dims[d];
+      o += c * stride[d];
+    }
+    return o;
+  }
+  }
+}
 
 __device__ __forceinline__ float ew_load(const void *p, long long i, int dt) {
   if (dt == 0) return reinterpret_cast<const float *>(p)[i];
@@ -60,13 +83,7 @@ __device__ __forceinline__ void ew_store(void *p, long long i, int dt, float v) 
 
 __global__ void binary_kernel(EwParams p, const void *a, const void *b, void *o) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
-    long long r = i, oa = 0, ob = 0;
-    for (int d = p.rank - 1; d >= 0; --d) {
-      const long long c = r % p.dims[d];
-      r /= p.dims[d];
-      oa += c * p.sa[d];
-      ob += c * p.sb[d];
-    }
+    const long long oa = ew_offset(p, i, p.mode_a, p.sa), ob = ew_offset(p, i, p.mode_b, p.sb);
     const float x = ew_load(a, oa, p.dt_a), y = ew_load(b, ob, p.dt_b);
     float v;
     switch (p.fn) {
@@ -81,12 +98,7 @@ __global__ void binary_kernel(EwParams p, const void *a, const void *b, void *o)
 
 __global__ void unary_kernel(EwParams p, const void *a, void *o) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
-    long long r = i, oa = 0;
-    for (int d = p.rank - 1; d >= 0; --d) {
-      const long long c = r % p.dims[d];
-      r /= p.dims[d];
-      oa += c * p.sa[d];
-    }
+    const long long oa = ew_offset(p, i, p.mode_a, p.sa);
     const float x = ew_load(a, oa, p.dt_a);
     float v;
     switch (p.fn) {
@@ -114,6 +126,7 @@ struct ReduceParams {
   int nr;
   int mean;
   int dt_a, dt_o;
+  int contiguous;   // the reduced elements of one output are consecutive in memory (innermost dims reduced)
 };
 
 // One thread per output element; the reduced indices are visited in ascending
@@ -151,13 +164,18 @@ __global__ void __launch_bounds__(256) reduce_block_kernel(ReduceParams p, const
       r /= p.kdims[d];
     }
     float s = 0.f;
-    for (long long j = threadIdx.x; j < p.red_total; j += 256) {
-      long long q = j, off = base;
-      for (int d = p.nr - 1; d >= 0; --d) {
-        off += (q % p.rdims[d]) * p.rstr[d];
-        q /= p.rdims[d];
+    if (p.contiguous) {
+#pragma unroll 4
+      for (long long j = threadIdx.x; j < p.red_total; j += 256) s = __fadd_rn(s, ew_load(a, base + j, p.dt_a));
+    } else {
+      for (long long j = threadIdx.x; j < p.red_total; j += 256) {
+        long long q = j, off = base;
+        for (int d = p.nr - 1; d >= 0; --d) {
+          off += (q % p.rdims[d]) * p.rstr[d];
+          q /= p.rdims[d];
+        }
+        s = __fadd_rn(s, ew_load(a, off, p.dt_a));
       }
-      s = __fadd_rn(s, ew_load(a, off, p.dt_a));
     }
     part[threadIdx.x] = s;
     __syncthreads();
@@ -617,8 +635,25 @@ struct dnnl_graph_compiler_executable {
           else throw std::invalid_argument("shapes are not broadcastable");
         }
       };
+      // offset shortcuts (only when the flat index fits 32 bits)
+      auto classify = [&](const long long *str) {
+        if (e.total >= (1ll << 31) || e.rank == 0) return 0;
+        const auto dense = dense_strides(O.shape);
+        bool same = true, none = true, row_vec = true, row_val = true;
+        for (int d = 0; d < e.rank; ++d) {
+          if (e.dims[d] == 1) continue;
+          const bool last = (d == e.rank - 1);
+          same &= (str[d] == dense[size_t(d)]);
+          none &= (str[d] == 0);
+          row_vec &= last ? (str[d] == 1) : (str[d] == 0);
+          row_val &= last ? (str[d] == 0) : (str[d] * e.dims[e.rank - 1] == dense[size_t(d)]);
+        }
+        return same ? 1 : none ? 2 : row_vec ? 3 : row_val ? 4 : 0;
+      };
+      e.inner = unsigned(e.rank ? e.dims[e.rank - 1] : 1);
       const LogicalTensor &A = p.tensors.at(st.in[0]);
       fill(A, e.sa);
+      e.mode_a = classify(e.sa);
       e.dt_a = ew_dtype(A.dtype);
       const int threads = 256;
       const int blocks = int(std::min<long long>((e.total + threads - 1) / threads, 148LL * 16));
@@ -626,6 +661,7 @@ struct dnnl_graph_compiler_executable {
       if (st.kind == StepKind::BINARY) {
         const LogicalTensor &B = p.tensors.at(st.in[1]);
         fill(B, e.sb);
+        e.mode_b = classify(e.sb);
         e.dt_b = ew_dtype(B.dtype);
         binary_kernel<<<blocks, threads, 0, s>>>(e, addr(st.in[0]), addr(st.in[1]), addr(st.out[0]));
       } else {
@@ -651,6 +687,16 @@ struct dnnl_graph_compiler_executable {
       }
       if (r.out_total != O.numel()) throw std::invalid_argument("reduce output shape does not match");
       r.mean = st.mean ? 1 : 0;
+      {
+        // reduced dims innermost and dense: element j of the reduction sits j elements after the first
+        long long expect = 1;
+        bool ok = r.nr > 0;
+        for (int d = r.nr - 1; d >= 0 && ok; --d) {
+          ok = (r.rstr[d] == expect);
+          expect *= r.rdims[d];
+        }
+        r.contiguous = ok ? 1 : 0;
+      }
       r.dt_a = ew_dtype(A.dtype);
       r.dt_o = ew_dtype(O.dtype);
       if (r.red_total >= 512 && r.out_total > 0) {
