@@ -70,6 +70,30 @@ __device__ __forceinline__ float ex2(float x) {
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// two f32 lanes per instruction (sm_100 packed f32x2 arithmetic)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 
 // Operand tiles in shared memory.  Q, K and P are K-major 128 x 128 bf16 tiles stored as two 128-row x
 // 128-byte swizzled blocks (contraction index 0..63 in block 0, 64..127 in block 1): K step j starts at
@@ -294,9 +318,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 128; ++i)
           if (i >= lim) sv[i] = 0xFF800000u;   // -inf
       }
-      float mx = -INFINITY;
+      float mx = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      for (int i = 0; i < 128; i += 4) {
+        mx = max3(mx, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+        mx_b = max3(mx_b, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+      }
+      mx = fmaxf(mx, mx_b);
       const float m_tile = mx * c;
       // lazy reference update: keep the old reference unless the maximum grew by more than 2^kLazy
       const bool grow = m_tile > m_used + kLazy;
@@ -327,21 +355,25 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       // ---- p = 2^(s*c - m_used), row sum, P -> shared memory (bf16, swizzled K-major)
-      float sum = 0.f;
-      const float neg_m = -m_used;
+      const uint64_t c2 = pack2(c, c), neg_m2 = pack2(-m_used, -m_used);
+      uint64_t sum2 = pack2(0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 16; ++k) {   // sixteen 16-byte chunks of 8 columns
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(sv[k * 8 + e * 2]), c, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(sv[k * 8 + e * 2 + 1]), c, neg_m));
-          sum += p0 + p1;
+          float x0, x1;
+          unpack2(fma2(pack2(__uint_as_float(sv[k * 8 + e * 2]), __uint_as_float(sv[k * 8 + e * 2 + 1])), c2, neg_m2), x0, x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);
+          sum2 = add2(sum2, pack2(p0, p1));
           w[e] = pack_bf16x2_rn(p0, p1);
         }
         // chunk k of the row: block (k >> 3), 16-byte slot (k & 7) ^ (row & 7)
         *reinterpret_cast<uint4 *>(pbuf + (k >> 3) * 16384 + (((k & 7) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      float sum, sum_hi;
+      unpack2(sum2, sum, sum_hi);
+      sum += sum_hi;
       l += sum;
       fence_proxy_async();     // P visible to the tensor core's shared-memory reads
       tc_fence_before();       // TMEM accesses above are ordered before the arrive
