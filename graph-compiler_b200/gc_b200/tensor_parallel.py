@@ -139,3 +139,84 @@ class TensorParallelMLP:
             planes = self.exchange.partial_planes(h, self.w[i + 1])          # row-parallel f32 partial sums, exchanged
             h = self.ops.epilogue(planes, self.b[i + 1], self.relu)          # reduce, cast, bias, ReLU
         return h
+
+
+# ------------------------------------------------------------------------------------------------
+# The other paths that shard: independent output columns (bf16 GEMM sweep, int8 GEMM) and independent
+# (batch, head) units (attention).  No exchange is needed to compute; the only collective is the optional
+# all-gather that reassembles the full result on every rank.
+class ShardedGemm:
+    """C = A . B with B (and C) split along N: rank r owns ``B[:, r-th block]`` and computes
+    ``C[:, r-th block]``; A is replicated.  ``gather=True`` all-gathers the column blocks."""
+
+    def __init__(self, B_shard, world: int, rank: int, ops=None, group=None):
+        self.B, self.world, self.rank, self.group = B_shard, world, rank, group
+        self.ops = ops if ops is not None else CudaOps()
+
+    def step(self, A, gather: bool = True):
+        import torch
+        import torch.distributed as dist
+
+        c = self.ops.linear(A, self.B, None, False)            # [M, N / world]
+        if not gather or self.world == 1:
+            return c
+        parts = [torch.empty_like(c) for _ in range(self.world)]
+        dist.all_gather(parts, c.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)
+
+
+class ShardedQuantGemm:
+    """u8 x s8 GEMM split along N: weights, scales, bias (and the zero-point compensation, which is a
+    per-column sum over K) all split with the columns, so every rank's block is complete by itself."""
+
+    def __init__(self, W_shard, scale_shard, bias_shard, zp: int, world: int, rank: int, ops=None, group=None):
+        self.W, self.scale, self.bias, self.zp = W_shard, scale_shard, bias_shard, zp
+        self.world, self.rank, self.group, self.ops = world, rank, group, ops
+
+    def step(self, A, gather: bool = True):
+        import torch
+        import torch.distributed as dist
+
+        if self.ops is not None:
+            c = self.ops.quant_linear(A, self.W, self.scale, self.bias, self.zp)
+        else:
+            from . import lib
+
+            comp = lib.colsum_s8(self.W, self.zp)          # zp * sum_k W[k, n]: per column, so it splits with N
+            c, _ = lib.matmul_u8s8(A, self.W, self.scale, self.bias, comp)
+        if not gather or self.world == 1:
+            return c
+        parts = [torch.empty_like(c) for _ in range(self.world)]
+        dist.all_gather(parts, c.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)
+
+
+def shard_heads(t, world: int, rank: int):
+    """[B, H, S, D] -> this rank's contiguous block of the B*H independent (batch, head) units, as [units, 1, S, D]."""
+    B, H, S, D = t.shape
+    lo, hi = shard_range(B * H, world, rank)
+    return t.reshape(B * H, 1, S, D)[lo:hi].contiguous()
+
+
+class ShardedAttention:
+    """Attention over (batch, head) units split across ranks; no collective on the data path."""
+
+    def __init__(self, world: int, rank: int, ops=None, group=None):
+        self.world, self.rank, self.ops, self.group = world, rank, ops, group
+
+    def step(self, Q, K, V, scale: float, causal: bool, gather: bool = False):
+        import torch
+        import torch.distributed as dist
+
+        q, k, v = (shard_heads(t, self.world, self.rank) for t in (Q, K, V))
+        if self.ops is not None:
+            o = self.ops.attention(q, k, v, scale, causal)
+        else:
+            from . import lib
+
+            o = lib.attention_bf16(q, k, v, scale, causal)
+        if not gather or self.world == 1:
+            return o
+        parts = [torch.empty_like(o) for _ in range(self.world)]
+        dist.all_gather(parts, o.contiguous(), group=self.group)
+        return torch.cat(parts, dim=0).reshape(Q.shape)

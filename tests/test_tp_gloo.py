@@ -105,3 +105,75 @@ def test_shard_helpers():
     assert ws[0].shape == (8, 3) and ws[1].shape == (3, 8) and bs[0].shape == (3,) and bs[1].shape == (8,)
     with pytest.raises(ValueError):
         TensorParallelMLP([W[0]], [None])
+
+
+# ------------------------------------------------------------------------------ the other sharded paths
+class _HostOps:
+    """CPU stand-ins for the kernels (exact integer-valued data, so results are bit-comparable)."""
+
+    def linear(self, x, w, b, relu):
+        return (x.float() @ w.float()).bfloat16()
+
+    def quant_linear(self, A, W, scale, bias, zp):
+        acc = A.to(torch.int32) @ W.to(torch.int32)
+        comp = zp * W.to(torch.int32).sum(0)
+        return (acc - comp).float() * scale + bias
+
+    def attention(self, q, k, v, scale, causal):
+        s = (q.float() @ k.float().transpose(-1, -2)) * scale
+        if causal:
+            S = s.shape[-1]
+            s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
+        return (torch.softmax(s, -1) @ v.float()).bfloat16()
+
+
+def _worker_sharded(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from gc_b200.tensor_parallel import ShardedAttention, ShardedGemm, ShardedQuantGemm
+
+        g = torch.Generator().manual_seed(1)
+        A = torch.randint(-3, 4, (16, 64), generator=g).bfloat16()
+        B = torch.randint(-2, 3, (64, 96), generator=g).bfloat16()
+        lo, hi = shard_range(96, world, rank)
+        c = ShardedGemm(B[:, lo:hi].contiguous(), world, rank, ops=_HostOps()).step(A)
+        Aq = torch.randint(0, 256, (8, 32), generator=g, dtype=torch.uint8)
+        Wq = torch.randint(-127, 128, (32, 48), generator=g, dtype=torch.int8)
+        sc, bi = torch.rand(48, generator=g), torch.randn(48, generator=g)
+        lo, hi = shard_range(48, world, rank)
+        cq = ShardedQuantGemm(Wq[:, lo:hi].contiguous(), sc[lo:hi], bi[lo:hi], 128, world, rank, ops=_HostOps()).step(Aq)
+        Q, K, V = (torch.randn(2, 4, 16, 8, generator=g).bfloat16() for _ in range(3))
+        o = ShardedAttention(world, rank, ops=_HostOps()).step(Q, K, V, 8 ** -0.5, True, gather=True)
+        q.put((rank, c.float().numpy(), cq.numpy(), o.float().numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_column_sharded_gemms_and_head_sharded_attention(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_worker_sharded, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict((r, rest) for r, *rest in (q.get(timeout=120) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    g = torch.Generator().manual_seed(1)
+    A = torch.randint(-3, 4, (16, 64), generator=g).bfloat16()
+    B = torch.randint(-2, 3, (64, 96), generator=g).bfloat16()
+    Aq = torch.randint(0, 256, (8, 32), generator=g, dtype=torch.uint8)
+    Wq = torch.randint(-127, 128, (32, 48), generator=g, dtype=torch.int8)
+    sc, bi = torch.rand(48, generator=g), torch.randn(48, generator=g)
+    Q, K, V = (torch.randn(2, 4, 16, 8, generator=g).bfloat16() for _ in range(3))
+    ops = _HostOps()
+    want = (ops.linear(A, B, None, False).float().numpy(), ops.quant_linear(Aq, Wq, sc, bi, 128).numpy(),
+            ops.attention(Q.reshape(8, 1, 16, 8), K.reshape(8, 1, 16, 8), V.reshape(8, 1, 16, 8), 8 ** -0.5, True).reshape(2, 4, 16, 8).float().numpy())
+    for r in range(world):
+        for got, w in zip(res[r], want):
+            assert np.array_equal(got, w), r      # every rank holds the full result, identical to one device
