@@ -392,15 +392,18 @@ def main():
 
         parallelism = "single GPU"
     else:
-        from gc_b200.tensor_parallel import AllReduceExchange, CudaOps, PeerPushExchange
+        from gc_b200.tensor_parallel import AllReduceExchange, CudaOps, PeerPushExchange, PeerReduceScatterExchange
 
         ws, bs = shard_weights([w.to(dev) for w in W_host], [b.to(dev) for b in B_host], world, rank)
         exchange, why = None, ""
-        if os.environ.get("GC_B200_EXCHANGE", "peer_push") == "peer_push":
+        # fused GEMM-epilogue exchanges: with two ranks sending the whole tile to the one peer is already minimal;
+        # beyond that the partial sums are reduce-scattered by rows and the result all-gathered
+        want = os.environ.get("GC_B200_EXCHANGE", "peer_push")
+        if want in ("peer_push", "peer_reduce_scatter"):
             try:
-                exchange = PeerPushExchange(BATCH, HIDDEN[-1], dev)
+                exchange = (PeerPushExchange if want == "peer_push" else PeerReduceScatterExchange)(BATCH, HIDDEN[-1], dev)
             except Exception as e:   # symmetric memory unavailable: NCCL all-reduce baseline
-                why = f" (peer push unavailable: {type(e).__name__})"
+                why = f" (fused exchange unavailable: {type(e).__name__})"
         if exchange is None:
             exchange = AllReduceExchange(CudaOps())
         tp = TensorParallelMLP(ws, bs, relu=True, exchange=exchange)
@@ -412,7 +415,7 @@ def main():
         graph, x_static = None, torch.empty_like(Xd)
         # Only with the peer-store exchange: a graph that holds NCCL kernels kept the communicator's
         # tear-down waiting at exit on this pool.
-        if os.environ.get("GC_B200_TP_GRAPH", "1") != "0" and exchange.name == "peer_push":
+        if os.environ.get("GC_B200_TP_GRAPH", "1") != "0" and exchange.name != "all_reduce":
             ok = 1
             try:
                 for _ in range(3):
@@ -454,8 +457,10 @@ def main():
             torch.cuda.current_stream().synchronize()
 
         parallelism = (f"tp{world}: layers 1,3 column-parallel, layers 2,4 row-parallel, f32 partial sums exchanged by "
-                       + ("GEMM-epilogue peer stores over NVLink + local reduce" if exchange.name == "peer_push"
-                          else "NCCL all-reduce") + ("; one CUDA-graph replay per step" if graph is not None else "") + why)
+                       + {"peer_push": "GEMM-epilogue peer stores over NVLink (every rank receives every partial sum) + local reduce",
+                          "peer_reduce_scatter": "GEMM-epilogue peer stores over NVLink to the row owner (reduce-scatter), owner reduces "
+                                                 "and stores the bf16 rows to every rank (all-gather)",
+                          "all_reduce": "NCCL all-reduce"}[exchange.name] + ("; one CUDA-graph replay per step" if graph is not None else "") + why)
     config["parallelism"] = parallelism
 
     def barrier():

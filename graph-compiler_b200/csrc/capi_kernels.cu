@@ -148,6 +148,29 @@ GCB_EXPORT int gcb200_matmul_bf16_f32out_push(const void *A, const void *B, void
   });
 }
 
+GCB_EXPORT int gcb200_matmul_bf16_f32out_scatter(const void *A, const void *B, void *const *peer_bufs, int n_peers, int my_plane,
+                                                 int64_t M, int64_t N, int64_t K, void *stream) {
+  return guarded([&] {
+    require(A && B && peer_bufs && n_peers >= 1 && n_peers <= 8 && my_plane >= 0, "bad arguments");
+    require(M > 0 && N > 0 && K > 0 && M % n_peers == 0, "M must be a positive multiple of the number of peers");
+    for (int d = 0; d < n_peers; ++d) require(peer_bufs[d] && (reinterpret_cast<uintptr_t>(peer_bufs[d]) & 15) == 0, "peer buffers must be 16-byte aligned");
+    if (!(tma_compatible(A, K, 2) && tma_compatible(B, N, 2))) throw std::logic_error("scatter matmul needs 16-byte aligned operand rows");
+    MatmulArgs a;
+    a.A = A; a.B = B; a.M = M; a.N = N; a.K = K;
+    a.out_kind = OUT_F32; a.out = peer_bufs[0];
+    a.n_peers = n_peers; a.peer_plane = my_plane; a.peer_out = peer_bufs; a.peer_rows = int(M / n_peers);
+    matmul_tc(a, static_cast<cudaStream_t>(stream));
+  });
+}
+
+GCB_EXPORT int gcb200_reduce_slice_broadcast_bf16(const float *parts, int nparts, int64_t rows, int64_t N, const void *bias,
+                                                  void *const *peer_out, int n_peers, int64_t row0, int relu, void *stream) {
+  return guarded([&] {
+    require(parts && peer_out, "bad arguments");
+    reduce_slice_broadcast_bf16(parts, nparts, rows, N, bias, peer_out, n_peers, row0, relu, static_cast<cudaStream_t>(stream));
+  });
+}
+
 GCB_EXPORT int gcb200_reduce_bias_act_bf16(const float *parts, int nparts, int64_t plane_stride, const void *bias,
                                            void *Y, int64_t M, int64_t N, int relu, void *stream) {
   return guarded([&] {

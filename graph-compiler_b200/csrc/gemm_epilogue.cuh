@@ -136,8 +136,15 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
           // into plane `peer_plane` of every rank's receive buffer (plain stores to peer memory over
           // NVLink), so the exchange overlaps the tiles still being computed.  Requires full
           // 16-byte chunks (checked by the launcher).
-          const size_t off = (size_t(p.peer_plane) * size_t(p.out_rows) + size_t(grow)) * ld_b + size_t(gcol) * esz;
-          for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[d]) + off) = val;
+          if (p.peer_rows > 0) {
+            // reduce-scatter by rows: only the rank that will reduce this row receives it
+            const int owner = grow / p.peer_rows, lrow = grow - owner * p.peer_rows;
+            const size_t off = (size_t(p.peer_plane) * size_t(p.peer_rows) + size_t(lrow)) * ld_b + size_t(gcol) * esz;
+            *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[owner]) + off) = val;
+          } else {
+            const size_t off = (size_t(p.peer_plane) * size_t(p.out_rows) + size_t(grow)) * ld_b + size_t(gcol) * esz;
+            for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[d]) + off) = val;
+          }
         } else if (vec_ok && nvalid == cpc) {
           *reinterpret_cast<uint4 *>(g) = val;
         } else {

@@ -46,6 +46,7 @@ struct GemmParams {
   int stages;
   int kpb;              // K blocks (of 128 bytes) per pipeline stage
   int group_m;          // rasterisation: tiles_m rows walked per column sweep
+  int prefetch_a, prefetch_b; // stages ahead of the copy at which the producer asks L2 to fetch the operand (0: off)
   OperandGeom a, b;
   uint32_t idesc;
   uint32_t tmem_cols;   // allocated TMEM columns (power of two >= 2*BN, >= 32)
@@ -65,6 +66,8 @@ struct GemmParams {
   // peer push (row-parallel layers): when n_peers > 0 the f32 tile is stored into plane `peer_plane`
   // of each of peer_out[0..n_peers) (buffers of [planes][out_rows][ld_out] f32) instead of `out`
   int n_peers, peer_plane;
+  int peer_rows;        // 0: every peer receives the whole tile; > 0: rows [d * peer_rows, (d + 1) * peer_rows) go to
+                        // peer d only, whose buffer is [planes][peer_rows][ld_out] (reduce-scatter by rows)
   void *peer_out[8];
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
   // TMA-store epilogue (one-CTA kernel, row-major orientation): tmC covers the output as

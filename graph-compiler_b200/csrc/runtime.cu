@@ -297,6 +297,12 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   p.splits = cfg.splits;
   p.stages = cfg.stages;
   p.group_m = cfg.group_m;
+  {
+    static const int pf_env = [] { const char *e = std::getenv("GC_B200_PREFETCH"); return e ? std::atoi(e) : -1; }();
+    const int pf = pf_env >= 0 ? pf_env : 0;
+    p.prefetch_a = pf;
+    p.prefetch_b = pf;
+  }
   p.BN = cfg.bn;
   p.out_rows = int(a.M);
   p.out_cols = int(a.N);
@@ -350,8 +356,10 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
       throw std::invalid_argument("peer push needs the f32-out row-major form, N % 4 == 0 and at most 8 peers");
     cfg.splits = 1;
     p.splits = 1;
+    if (a.peer_rows > 0 && (a.peer_rows * a.n_peers != a.M)) throw std::invalid_argument("row scatter needs M = peers x rows per peer");
     p.n_peers = a.n_peers;
     p.peer_plane = a.peer_plane;
+    p.peer_rows = a.peer_rows;
     for (int d = 0; d < a.n_peers; ++d) p.peer_out[d] = a.peer_out[d];
   }
   const bool split = cfg.splits > 1;
@@ -502,6 +510,62 @@ reduce_planes_bf16x4_kernel(const float4 *parts, int nparts, long long plane4, u
     if (relu) { lo = bf16x2_relu(lo); hi = bf16x2_relu(hi); }
     out[i] = make_uint2(bf16x2_fix_nan(lo), bf16x2_fix_nan(hi));
   }
+}
+
+struct PeerPtrs { uint2 *p[8]; };
+// The reduction of one rank's row slice, stored into every peer's result buffer (see runtime.h).
+__global__ void __launch_bounds__(256)
+reduce_slice_bcast_kernel(const float4 *parts, int nparts, long long plane4, long long total4, int n4, const uint2 *bias,
+                          int relu, PeerPtrs out, int n_peers, long long dst4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    float4 s = parts[i];
+    for (int k = 1; k < nparts; ++k) {
+      const float4 t = parts[(long long)k * plane4 + i];
+      s.x = __fadd_rn(s.x, t.x); s.y = __fadd_rn(s.y, t.y); s.z = __fadd_rn(s.z, t.z); s.w = __fadd_rn(s.w, t.w);
+    }
+    uint32_t lo = pack_bf16x2_rn(s.x, s.y), hi = pack_bf16x2_rn(s.z, s.w);
+    if (bias) {
+      const uint2 b = bias[int(i % n4)];
+      lo = pack_bf16x2_rn(__fadd_rn(__uint_as_float(lo << 16), __uint_as_float(b.x << 16)),
+                          __fadd_rn(__uint_as_float(lo & 0xFFFF0000u), __uint_as_float(b.x & 0xFFFF0000u)));
+      hi = pack_bf16x2_rn(__fadd_rn(__uint_as_float(hi << 16), __uint_as_float(b.y << 16)),
+                          __fadd_rn(__uint_as_float(hi & 0xFFFF0000u), __uint_as_float(b.y & 0xFFFF0000u)));
+    }
+    if (relu) { lo = bf16x2_relu(lo); hi = bf16x2_relu(hi); }
+    const uint2 v = make_uint2(bf16x2_fix_nan(lo), bf16x2_fix_nan(hi));
+    for (int d = 0; d < n_peers; ++d) out.p[d][dst4 + i] = v;
+  }
+}
+
+void reduce_slice_broadcast_bf16(const float *parts, int nparts, int64_t rows, int64_t N, const void *bias_bf16,
+                                 void *const *peer_out, int n_peers, int64_t row0, int relu, cudaStream_t stream) {
+  DeviceState &dev = device_state();
+  auto al = [](const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) & (a - 1)) == 0; };
+  if (nparts < 1 || n_peers < 1 || n_peers > 8 || rows <= 0 || N <= 0 || N % 4 || !al(parts, 16) || (bias_bf16 && !al(bias_bf16, 8)))
+    throw std::invalid_argument("reduce_slice_broadcast: N must be a multiple of 4, planes 16-byte and bias 8-byte aligned, 1..8 peers");
+  PeerPtrs pp{};
+  for (int d = 0; d < n_peers; ++d) {
+    if (!peer_out[d] || !al(peer_out[d], 8)) throw std::invalid_argument("reduce_slice_broadcast: peer buffers must be 8-byte aligned");
+    pp.p[d] = reinterpret_cast<uint2 *>(peer_out[d]);
+  }
+  const long long total4 = rows * N / 4;
+  const int threads = 256;
+  const int blocks = int(std::min<long long>((total4 + threads - 1) / threads, (long long)dev.sm_count * 8));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(std::max(blocks, 1)));
+  cfg.blockDim = dim3(threads);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  GCB_CUDA(cudaLaunchKernelEx(&cfg, reduce_slice_bcast_kernel, reinterpret_cast<const float4 *>(parts), nparts, (long long)(rows * N / 4),
+                              total4, int(N / 4), reinterpret_cast<const uint2 *>(bias_bf16), relu, pp, n_peers,
+                              (long long)(row0 * N / 4)));
+  count_launch();
 }
 
 void reduce_planes(const void *parts, int nparts, int64_t plane, void *out, int64_t M, int64_t N, int out_kind,

@@ -91,6 +91,7 @@ struct MatmulArgs {
   int relu = 0;
   int n_peers = 0;              // > 0: push the f32 result into plane `peer_plane` of each peer buffer
   int peer_plane = 0;
+  int peer_rows = 0;            // > 0: rows are scattered to their owner (row / peer_rows) instead of sent to every peer
   void *const *peer_out = nullptr;
   const MatmulConfig *force = nullptr; // optional override
   void *scratch = nullptr;      // optional caller-provided split-K scratch (else the device workspace)
@@ -115,6 +116,10 @@ void matmul_simt(const void *A, const void *B, const void *bias, void *out, int6
 int read_device_error(cudaStream_t stream); // synchronises the stream; returns and clears the error word
 
 // Kernel launches issued by this library since load (every launcher counts its own).
+// Sum `nparts` f32 planes of a [rows, N] slice in plane order, bias + ReLU + cast, and store the bf16 slice
+// at row `row0` of the [*, N] result buffer of EVERY peer (plain stores; the all-gather half of an all-reduce).
+void reduce_slice_broadcast_bf16(const float *parts, int nparts, int64_t rows, int64_t N, const void *bias_bf16,
+                                 void *const *peer_out, int n_peers, int64_t row0, int relu, cudaStream_t stream);
 void count_launch(int n = 1);
 unsigned long long launch_count();
 

@@ -56,6 +56,8 @@ def load() -> C.CDLL:
         "gcb200_matmul_bf16_f32out": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
         "gcb200_matmul_bf16_f32out_push": [_vp, _vp, C.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp],
         "gcb200_reduce_bias_act_bf16": [_vp, _int, _i64, _vp, _vp, _i64, _i64, _int, _vp],
+        "gcb200_matmul_bf16_f32out_scatter": [_vp, _vp, C.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp],
+        "gcb200_reduce_slice_broadcast_bf16": [_vp, _int, _i64, _i64, _vp, C.POINTER(_vp), _int, _i64, _int, _vp],
         "gcb200_matmul_u8s8": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp],
         "gcb200_colsum_s8": [_vp, _vp, _i64, _i64, _i32, _vp],
         "gcb200_matmul_f32": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
@@ -153,6 +155,22 @@ def matmul_bf16_f32out_push(A, B, peer_ptrs, my_plane: int):
     N = B.shape[1]
     arr = (_vp * len(peer_ptrs))(*peer_ptrs)
     check(load().gcb200_matmul_bf16_f32out_push(_ptr(A), _ptr(B), arr, len(peer_ptrs), my_plane, M, N, K, _stream()))
+
+
+def matmul_bf16_f32out_scatter(A, B, peer_ptrs, my_plane: int):
+    """Row block d of the f32 partial sums of A.B goes into plane ``my_plane`` of peer d's buffer [g][M/g][N] only."""
+    M, K = A.shape
+    N = B.shape[1]
+    arr = (_vp * len(peer_ptrs))(*peer_ptrs)
+    check(load().gcb200_matmul_bf16_f32out_scatter(_ptr(A), _ptr(B), arr, len(peer_ptrs), my_plane, M, N, K, _stream()))
+
+
+def reduce_slice_broadcast_bf16(parts, bias, relu, out_ptrs, row0: int):
+    """parts: this rank's f32 [g, rows, N]; the reduced bf16 rows land at row ``row0`` of every buffer in ``out_ptrs``."""
+    nparts, rows, N = parts.shape
+    arr = (_vp * len(out_ptrs))(*out_ptrs)
+    check(load().gcb200_reduce_slice_broadcast_bf16(_ptr(parts), nparts, rows, N, _ptr(bias), arr, len(out_ptrs), row0, int(relu),
+                                                    _stream()))
 
 
 def reduce_bias_act_bf16(parts, bias=None, relu=False, out=None):

@@ -65,7 +65,7 @@ class CudaOps:
 
 
 class AllReduceExchange:
-    """Baseline exchange: local f32 partial sums, then one NCCL/gloo all-reduce."""
+    """Baseline exchange: local f32 partial sums, one NCCL/gloo all-reduce, then the epilogue on every rank."""
 
     name = "all_reduce"
     launches_per_pair = 3
@@ -73,21 +73,21 @@ class AllReduceExchange:
     def __init__(self, ops, group=None):
         self.ops, self.group = ops, group
 
-    def partial_planes(self, x, w):
+    def row_parallel(self, x, w, bias, relu):
         import torch.distributed as dist
 
         part = self.ops.linear_partial(x, w)
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
-        return part.unsqueeze(0)
+        return self.ops.epilogue(part.unsqueeze(0), bias, relu)
 
 
 class PeerPushExchange:
-    """Fused exchange: the GEMM epilogue stores this rank's partial sums into plane `rank` of every
-    rank's receive buffer (peer-mapped symmetric memory, plain NVLink stores), one cross-rank barrier,
-    then every rank reduces its g planes locally in rank order.  Two receive buffers alternate so that
-    a buffer is only overwritten after the barrier of the following exchange, i.e. after every rank has
-    finished reading it."""
+    """Fused exchange, all-to-all form: the GEMM epilogue stores this rank's partial sums into plane `rank` of
+    every rank's receive buffer (peer-mapped symmetric memory, plain NVLink stores), one cross-rank barrier,
+    then every rank reduces its g planes locally in rank order.  Every partial sum crosses NVLink g - 1 times:
+    fine for two ranks, wasteful beyond (see PeerReduceScatterExchange).  Two receive buffers alternate so that
+    a buffer is only overwritten after the barrier of the following exchange."""
 
     name = "peer_push"
     launches_per_pair = 3
@@ -111,12 +111,58 @@ class PeerPushExchange:
             self.ptrs.append([int(p) for p in h.buffer_ptrs])
         self.turn = 0
 
-    def partial_planes(self, x, w):
+    def row_parallel(self, x, w, bias, relu):
         i = self.turn
         self.turn ^= 1
         self._lib.matmul_bf16_f32out_push(x, w, self.ptrs[i], self.rank)
         self.hdls[i].barrier(channel=0)   # every rank's stores have landed and are visible
-        return self.bufs[i]
+        return self._lib.reduce_bias_act_bf16(self.bufs[i], bias, relu=relu)
+
+
+class PeerReduceScatterExchange:
+    """Fused exchange with an all-reduce's traffic.  The GEMM epilogue stores row block d of this rank's f32
+    partial sums into peer d's receive buffer only (reduce-scatter by rows, overlapped with the tiles still
+    being computed); barrier; rank d sums the g planes of its rows in rank order, applies bias / ReLU, casts
+    once and stores the bf16 rows into EVERY rank's result buffer (all-gather by peer stores); barrier.  Per
+    GPU (g - 1)/g of the f32 partial sums and (g - 1)/g of the bf16 result cross NVLink, instead of g - 1
+    copies of the partial sums.  Every rank ends with identical bits: each row is reduced exactly once.
+    Result buffers alternate so that a step's output survives the next exchange."""
+
+    name = "peer_reduce_scatter"
+    launches_per_pair = 3
+
+    def __init__(self, M: int, N: int, device, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import lib
+
+        self._lib = lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if M % self.world:
+            raise ValueError(f"{M} rows are not divisible by {self.world} ranks")
+        self.rows = M // self.world
+        self.recv = symm.empty((self.world, self.rows, N), dtype=torch.float32, device=device)
+        self.recv_h = symm.rendezvous(self.recv, self.group)
+        self.recv_ptrs = [int(p) for p in self.recv_h.buffer_ptrs]
+        self.outs, self.out_ptrs = [], []
+        for _ in range(2):
+            t = symm.empty((M, N), dtype=torch.bfloat16, device=device)
+            h = symm.rendezvous(t, self.group)
+            self.outs.append(t)
+            self.out_ptrs.append([int(p) for p in h.buffer_ptrs])
+        self.turn = 0
+
+    def row_parallel(self, x, w, bias, relu):
+        i = self.turn
+        self.turn ^= 1
+        self._lib.matmul_bf16_f32out_scatter(x, w, self.recv_ptrs, self.rank)
+        self.recv_h.barrier(channel=0)   # my rows of every rank's partial sums have landed
+        self._lib.reduce_slice_broadcast_bf16(self.recv, bias, relu, self.out_ptrs[i], self.rank * self.rows)
+        self.recv_h.barrier(channel=1)   # every rank's rows of the result have landed here; recv is free again
+        return self.outs[i]
 
 
 class TensorParallelMLP:
@@ -135,9 +181,8 @@ class TensorParallelMLP:
     def step(self, x):
         h = x
         for i in range(0, len(self.w), 2):
-            h = self.ops.linear(h, self.w[i], self.b[i], self.relu)          # column-parallel, local post-ops
-            planes = self.exchange.partial_planes(h, self.w[i + 1])          # row-parallel f32 partial sums, exchanged
-            h = self.ops.epilogue(planes, self.b[i + 1], self.relu)          # reduce, cast, bias, ReLU
+            h = self.ops.linear(h, self.w[i], self.b[i], self.relu)                       # column-parallel, local post-ops
+            h = self.exchange.row_parallel(h, self.w[i + 1], self.b[i + 1], self.relu)   # row-parallel: partial sums, exchange, epilogue
         return h
 
 

@@ -81,6 +81,17 @@ int gcb200_matmul_bf16_f32out(const void *A, const void *B, float *Y, int64_t M,
 int gcb200_matmul_bf16_f32out_push(const void *A, const void *B, void *const *peer_bufs, int n_peers, int my_plane,
                                    int64_t M, int64_t N, int64_t K, void *stream);
 
+/* The same layer with the exchange shaped as reduce-scatter + all-gather (an all-reduce's traffic instead
+ * of g copies of every partial sum): row block d of the f32 partial sums, rows [d M/g, (d+1) M/g), is stored
+ * by the GEMM epilogue into plane `my_plane` of peer d's buffer [g][M/g][N] f32 only.  After a barrier rank d
+ * calls gcb200_reduce_slice_broadcast_bf16 on its own buffer: planes summed in rank order, bias, ReLU, one
+ * cast, and the bf16 rows are stored at row `row0` = d M/g of EVERY rank's [M,N] result buffer
+ * (peer_out[0..n_peers)); after a second barrier every rank holds the whole layer output, bit-identical. */
+int gcb200_matmul_bf16_f32out_scatter(const void *A, const void *B, void *const *peer_bufs, int n_peers, int my_plane,
+                                      int64_t M, int64_t N, int64_t K, void *stream);
+int gcb200_reduce_slice_broadcast_bf16(const float *parts, int nparts, int64_t rows, int64_t N, const void *bias,
+                                       void *const *peer_out, int n_peers, int64_t row0, int relu, void *stream);
+
 /* Sum `nparts` f32 planes [M,N] (`plane_stride` elements apart) in plane order,
  * then apply the bf16 epilogue bf16(bf16(sum)+bias), ReLU.  The reduce + cast
  * step of the K-split form (DeepTileContractionOp.cpp:446-471). */

@@ -1,6 +1,6 @@
-"""Tensor-parallel MLP on real GPUs (needs >= 2 devices; skipped otherwise): the fused
-GEMM-epilogue peer-store exchange and the NCCL all-reduce baseline against the oracle's
-single-device chain.  Ranks are child processes, one per GPU; NVLS is switched off and the
+"""Tensor-parallel MLP on real GPUs (needs >= 2 devices; skipped otherwise): the two fused
+GEMM-epilogue peer-store exchanges (all-to-all and reduce-scatter + all-gather) and the NCCL
+all-reduce baseline against the oracle's single-device chain.  Ranks are child processes, one per GPU; NVLS is switched off and the
 kernels use plain peer stores, so a rank that fails cannot fault its peers' GPUs."""
 import os
 import socket
@@ -35,7 +35,8 @@ def _worker(rank, world, port, mode, q):
     import torch.distributed as dist
 
     from gc_b200 import lib
-    from gc_b200.tensor_parallel import AllReduceExchange, CudaOps, PeerPushExchange, TensorParallelMLP, shard_weights
+    from gc_b200.tensor_parallel import (AllReduceExchange, CudaOps, PeerPushExchange, PeerReduceScatterExchange,
+                                         TensorParallelMLP, shard_weights)
 
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -43,16 +44,17 @@ def _worker(rank, world, port, mode, q):
     try:
         X, Ws, Bs = _make()
         ws, bs = shard_weights([w.to(dev) for w in Ws], [b.to(dev) for b in Bs], world, rank)
-        ex = PeerPushExchange(BATCH, HIDDEN[2], dev) if mode == "peer_push" else AllReduceExchange(CudaOps())
+        fused = {"peer_push": PeerPushExchange, "peer_reduce_scatter": PeerReduceScatterExchange}.get(mode)
+        ex = fused(BATCH, HIDDEN[2], dev) if fused else AllReduceExchange(CudaOps())
         # the two row-parallel layers have different widths: one exchange object per width
-        ex2 = PeerPushExchange(BATCH, HIDDEN[4], dev) if mode == "peer_push" else ex
+        ex2 = fused(BATCH, HIDDEN[4], dev) if fused else ex
         tp1 = TensorParallelMLP(ws[:2], bs[:2], relu=True, exchange=ex)
         tp2 = TensorParallelMLP(ws[2:], bs[2:], relu=True, exchange=ex2)
         outs = []
         for _ in range(3):                     # repeated steps exercise the alternating receive buffers
             y = tp2.step(tp1.step(X.to(dev)))
             torch.cuda.synchronize()
-            outs.append(_bits(y).copy())
+            outs.append(_bits(y).copy())          # copied out at once: the exchange's result buffers alternate
         assert lib.device_error() == 0
         q.put((rank, outs))
     finally:
@@ -65,7 +67,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("mode", ["all_reduce", "peer_push"])
+@pytest.mark.parametrize("mode", ["all_reduce", "peer_push", "peer_reduce_scatter"])
 def test_tensor_parallel_mlp_on_gpus(mode):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
