@@ -115,7 +115,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t boxes = g.boxes, box_bytes = g.box_bytes, box_mn = g.box_mn;
       const bool mn = g.mn_major != 0, one = g.one_load != 0, k3d = g.k3d != 0;
       const int bk = p.bk_elems, kpb = max(p.kpb, 1);
-      const int pf = is_a ? p.prefetch_a : p.prefetch_b;
       int err = 0;
       for (int u = blockIdx.x; u < units && !err; u += gridDim.x) {
         const int tile = u / p.splits, split = u - tile * p.splits;
@@ -138,23 +137,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             tma_load_3d(dst, tm, full, 0, k_off, grp);
           } else {
             for (uint32_t i = 0; i < boxes; ++i) tma_load_2d(dst + i * box_bytes, tm, full, mn_off + int(i * box_mn), k_off);
-          }
-          if (pf > 0) {
-            // ask L2 for the stage `pf` stages ahead (same tile): an operand streamed from HBM then arrives
-            // with L2 latency when its copy is issued
-            const int kb_f = kb + pf * kpb;
-            if (kb_f < kb1) {
-              const int k_f = k_off + pf * kpb * bk;
-              if (!mn) {
-                if (k3d) tma_prefetch_3d(tm, 0, mn_off, kb_f);
-                else
-                  for (uint32_t i = 0; i < boxes; ++i) tma_prefetch_2d(tm, k_f + int(i) * bk, mn_off);
-              } else if (one) {
-                tma_prefetch_3d(tm, 0, k_f, grp);
-              } else {
-                for (uint32_t i = 0; i < boxes; ++i) tma_prefetch_2d(tm, mn_off + int(i * box_mn), k_f);
-              }
-            }
           }
           if (++s == stages) { s = 0; ph ^= 1u; }
         }

@@ -46,7 +46,6 @@ struct GemmParams {
   int stages;
   int kpb;              // K blocks (of 128 bytes) per pipeline stage
   int group_m;          // rasterisation: tiles_m rows walked per column sweep
-  int prefetch_a, prefetch_b; // stages ahead of the copy at which the producer asks L2 to fetch the operand (0: off)
   OperandGeom a, b;
   uint32_t idesc;
   uint32_t tmem_cols;   // allocated TMEM columns (power of two >= 2*BN, >= 32)

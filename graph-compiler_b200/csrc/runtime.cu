@@ -297,12 +297,6 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   p.splits = cfg.splits;
   p.stages = cfg.stages;
   p.group_m = cfg.group_m;
-  {
-    static const int pf_env = [] { const char *e = std::getenv("GC_B200_PREFETCH"); return e ? std::atoi(e) : -1; }();
-    const int pf = pf_env >= 0 ? pf_env : 0;
-    p.prefetch_a = pf;
-    p.prefetch_b = pf;
-  }
   p.BN = cfg.bn;
   p.out_rows = int(a.M);
   p.out_cols = int(a.N);

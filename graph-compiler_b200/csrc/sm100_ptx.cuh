@@ -100,16 +100,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// Tiled prefetch into L2 only (no shared-memory destination, no barrier).
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *m, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *m, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y),
-               "r"(z)
-               : "memory");
-}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(m)),
