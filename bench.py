@@ -302,6 +302,82 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "aut
     return r
 
 
+def run_sharded_case(spec: str, steps: int, warmup: int, rank: int, world: int):
+    """The kernel-level cases that shard across GPUs (one process per GPU, launched under torchrun):
+    gemm:M:N:K and int8:M:N:K split along N with the all-gather of C done by the GEMM epilogue (peer stores; set
+    GC_B200_GATHER=nccl for the library all-gather), decode (the same with the weight-stationary kernel), attention:B:H:S:D:causal split by (batch, head) with no collective.  Inputs are resident before
+    timing; the time is the maximum over ranks of a CUDA-event bracket around `steps` steps."""
+    import math
+
+    import torch
+    import torch.distributed as dist
+
+    from gc_b200 import lib
+    from gc_b200.tensor_parallel import PeerGatherGemm, ShardedAttention, ShardedGemm, ShardedQuantGemm, shard_range
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(0)          # same seed on every rank: replicated inputs are identical
+    f = spec.split(":")
+    kind = f[0]
+    fused = os.environ.get("GC_B200_GATHER", "peer") != "nccl"
+    how = "n/a"
+    if kind in ("gemm", "decode"):
+        M, N, K = (16, 28672, 8192) if kind == "decode" else map(int, f[1:4])
+        lo, hi = shard_range(N, world, rank)
+        A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).bfloat16()
+        Bs = (torch.rand((K, N), generator=g, device=dev) * 2 - 1).bfloat16()[:, lo:hi].contiguous()
+        if fused:
+            op = PeerGatherGemm(Bs, M, N, dev)
+            fn, how = (lambda: op.step(A)), "all-gather of C by peer stores from the GEMM epilogue + one barrier"
+        else:
+            op = ShardedGemm(Bs, world, rank)
+            fn, how = (lambda: op.step(A, gather=True)), "NCCL all-gather of C"
+        work, unit = 2.0 * M * N * K, "TFLOPS"
+    elif kind == "int8":
+        M, N, K = map(int, f[1:4])
+        lo, hi = shard_range(N, world, rank)
+        A = torch.randint(0, 256, (M, K), generator=g, device=dev, dtype=torch.uint8)
+        W = torch.randint(-127, 128, (K, N), generator=g, device=dev, dtype=torch.int8)[:, lo:hi].contiguous()
+        sc = (torch.rand(N, generator=g, device=dev) * 0.009 + 0.001)[lo:hi].contiguous()
+        bi = (torch.rand(N, generator=g, device=dev) * 2 - 1)[lo:hi].contiguous()
+        if fused:
+            op = PeerGatherGemm(W, M, N, dev, bias_shard=bi, quant=(sc, 128))
+            fn, how = (lambda: op.step(A)), "all-gather of C by peer stores from the GEMM epilogue + one barrier"
+        else:
+            op = ShardedQuantGemm(W, sc, bi, 128, world, rank)
+            fn, how = (lambda: op.step(A, gather=True)), "NCCL all-gather of C"
+        work, unit = 2.0 * M * N * K, "TOPS"
+    elif kind == "attention":
+        B_, H, S, D, causal = map(int, f[1:6])
+        units = shard_range(B_ * H, world, rank)
+        n = units[1] - units[0]
+        Q, Kt, V = (torch.randn(n, 1, S, D, generator=g, device=dev).bfloat16() for _ in range(3))   # this rank's units, resident
+        O = torch.empty_like(Q)
+        fn, how = (lambda: lib.attention_bf16(Q, Kt, V, 1.0 / math.sqrt(D), bool(causal), out=O)), "no collective ((batch, head) units are independent)"
+        work, unit = 4.0 * B_ * H * S * S * D * (0.5 if causal else 1.0), "TFLOPS"
+    else:
+        raise ValueError(f"{spec} does not shard")
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    l0 = lib.launch_count()
+    st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    st.record()
+    for _ in range(steps):
+        fn()
+    en.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([st.elapsed_time(en) / steps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    assert lib.device_error() == 0
+    return {"case": spec, "n_gpus": world, "ms": ms, "value": work / ms / 1e9, "unit": unit, "scaling": "strong",
+            "launches_per_step_per_rank": int((lib.launch_count() - l0) // steps), "collective": how,
+            "timing": "CUDA events, max over ranks, inputs resident"}
+
+
 SWEEP = ["cfg1", "int8:1024:4096:4096", "decode", "attention:16:32:2048:128:0", "attention:16:32:2048:128:1", "gemm:1024:1024:1024",
          "gemm:2048:2048:2048", "gemm:4096:4096:4096", "gemm:8192:8192:8192", "gemm:16384:16384:16384"]
 
@@ -346,6 +422,18 @@ def main():
         import torch
 
         torch.cuda.set_device(local_rank)
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            try:
+                r = run_sharded_case(a.case, a.steps, a.warmup, rank, world)
+                if rank == 0:
+                    print(json.dumps(r))
+                torch.cuda.synchronize()
+            finally:
+                dist.destroy_process_group()
+            return
         print(json.dumps(run_case(a.case, a.steps, a.warmup, a.flush)))
         return
 

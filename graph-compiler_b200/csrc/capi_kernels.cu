@@ -8,6 +8,7 @@
 
 #include "../../include/gc_b200.h"
 #include "runtime.h"
+#include "tune_cache.h"
 #include "sm100_ptx.cuh"
 
 #define GCB_EXPORT extern "C" __attribute__((visibility("default")))
@@ -200,6 +201,42 @@ GCB_EXPORT int gcb200_matmul_u8s8(const void *A, const void *W, const float *sca
   });
 }
 
+GCB_EXPORT int gcb200_matmul_bf16_allgather(const void *A, const void *B, const void *bias, void *const *peer_C, int n_peers,
+                                            int64_t M, int64_t N, int64_t K, int64_t ldc, int transpose_a, int transpose_b,
+                                            int relu, void *stream) {
+  return guarded([&] {
+    require(A && B && peer_C && n_peers >= 1 && n_peers <= 8, "bad arguments");
+    require(M > 0 && N > 0 && K > 0 && ldc >= N, "all-gather matmul needs positive M, N, K and ldc >= N");
+    for (int d = 0; d < n_peers; ++d) require(peer_C[d] && (reinterpret_cast<uintptr_t>(peer_C[d]) & 15) == 0, "peer buffers must be 16-byte aligned");
+    if (!(tma_compatible(A, transpose_a ? M : K, 2) && tma_compatible(B, transpose_b ? K : N, 2)))
+      throw std::logic_error("all-gather matmul needs 16-byte aligned operand rows");
+    MatmulArgs a;
+    a.A = A; a.B = B; a.M = M; a.N = N; a.K = K; a.trans_a = transpose_a; a.trans_b = transpose_b;
+    a.out_kind = OUT_BF16; a.out = peer_C[0]; a.ld_out = ldc;
+    a.bias_kind = bias ? BIAS_BF16 : BIAS_NONE; a.bias = bias; a.relu = relu;
+    a.n_peers = n_peers; a.peer_out = peer_C;
+    matmul_tc(a, static_cast<cudaStream_t>(stream));
+  });
+}
+
+GCB_EXPORT int gcb200_matmul_u8s8_allgather(const void *A, const void *W, const float *scale, const float *bias,
+                                            const int32_t *comp, void *const *peer_C, int n_peers, int64_t M, int64_t N,
+                                            int64_t K, int64_t ldc, int transpose_b, void *stream) {
+  return guarded([&] {
+    require(A && W && scale && peer_C && n_peers >= 1 && n_peers <= 8, "bad arguments");
+    require(M > 0 && N > 0 && K > 0 && ldc >= N, "all-gather matmul needs positive M, N, K and ldc >= N");
+    for (int d = 0; d < n_peers; ++d) require(peer_C[d] && (reinterpret_cast<uintptr_t>(peer_C[d]) & 15) == 0, "peer buffers must be 16-byte aligned");
+    if (!(tma_compatible(A, K, 1) && tma_compatible(W, transpose_b ? K : N, 1)))
+      throw std::logic_error("int8 matmul needs K and N to be multiples of 16 and 16-byte aligned bases");
+    MatmulArgs a;
+    a.A = A; a.B = W; a.M = M; a.N = N; a.K = K; a.int8 = 1; a.trans_b = transpose_b;
+    a.out_kind = OUT_DEQUANT_F32; a.out = peer_C[0]; a.ld_out = ldc; a.scale = scale; a.comp = comp;
+    a.bias_kind = bias ? BIAS_F32 : BIAS_NONE; a.bias = bias;
+    a.n_peers = n_peers; a.peer_out = peer_C;
+    matmul_tc(a, static_cast<cudaStream_t>(stream));
+  });
+}
+
 GCB_EXPORT int gcb200_colsum_s8(const void *W, int32_t *comp, int64_t K, int64_t N, int32_t zp_a, void *stream) {
   return guarded([&] {
     require(W && comp && K > 0 && N > 0, "bad arguments");
@@ -224,6 +261,59 @@ GCB_EXPORT int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int 
     MatmulConfig c = select_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count);
     *cfg = gcb200_matmul_config{c.swapped, c.bn, c.splits, c.stages, c.group_m, c.grid, c.pair, c.kpb};
   });
+}
+
+GCB_EXPORT int gcb200_model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count,
+                                          gcb200_matmul_config *cfg) {
+  return guarded([&] {
+    require(cfg && M > 0 && N > 0 && K > 0 && sm_count > 0, "bad arguments");
+    require(dtype_bytes == 1 || dtype_bytes == 2, "dtype_bytes must be 1 or 2");
+    MatmulConfig c = model_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count);
+    *cfg = gcb200_matmul_config{c.swapped, c.bn, c.splits, c.stages, c.group_m, c.grid, c.pair, c.kpb};
+  });
+}
+
+GCB_EXPORT int gcb200_tune_cache_put(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes,
+                                     const gcb200_matmul_config *cfg) {
+  return guarded([&] {
+    require(cfg, "bad arguments");
+    tune::put(tune::Key{M, N, K, dtype_bytes, out_bytes},
+              MatmulConfig{cfg->swapped, cfg->bn, cfg->splits, cfg->stages, cfg->group_m, cfg->grid, cfg->pair, cfg->kpb});
+  });
+}
+
+GCB_EXPORT int gcb200_tune_cache_get(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, gcb200_matmul_config *cfg,
+                                     int *found) {
+  return guarded([&] {
+    require(cfg && found, "bad arguments");
+    MatmulConfig c{};
+    *found = tune::lookup(tune::Key{M, N, K, dtype_bytes, out_bytes}, &c) ? 1 : 0;
+    if (*found) *cfg = gcb200_matmul_config{c.swapped, c.bn, c.splits, c.stages, c.group_m, c.grid, c.pair, c.kpb};
+  });
+}
+
+GCB_EXPORT int gcb200_tune_cache_load(const char *path, int *entries_read) {
+  return guarded([&] {
+    require(path, "bad arguments");
+    const int n = tune::load(path);
+    if (entries_read) *entries_read = n;
+  });
+}
+
+GCB_EXPORT int gcb200_tune_cache_save(const char *path, int *entries_written) {
+  return guarded([&] {
+    require(path, "bad arguments");
+    const int n = tune::save(path);
+    if (entries_written) *entries_written = n;
+  });
+}
+
+GCB_EXPORT int gcb200_tune_cache_erase(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes) {
+  return guarded([&] { tune::erase(tune::Key{M, N, K, dtype_bytes, out_bytes}); });
+}
+
+GCB_EXPORT int gcb200_tune_cache_clear(void) {
+  return guarded([&] { tune::clear(); });
 }
 
 // ----------------------------------------------------------------------------- brgemm runtime ABI

@@ -192,12 +192,20 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
           if (p.bias_kind == BIAS_BF16)
             y = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(y), bf16_bits_to_f32(bias_bits)));
           if (p.relu) { const float f = bf16_bits_to_f32(y); y = (f != f) ? y : (f > 0.f ? y : 0u); }
-          reinterpret_cast<uint16_t *>(p.out)[idx] = uint16_t(y);
+          if (p.n_peers > 0) {   // column-sharded across GPUs: the finished element goes to every rank's result
+            for (int d = 0; d < p.n_peers; ++d) reinterpret_cast<uint16_t *>(p.peer_out[d])[idx] = uint16_t(y);
+          } else {
+            reinterpret_cast<uint16_t *>(p.out)[idx] = uint16_t(y);
+          }
         } else if (p.out_kind == OUT_DEQUANT_F32) {
           float f = __fmul_rn(float(int32_t(v[j]) - comp_i), scale_f);
           if (p.bias_kind == BIAS_F32) f = __fadd_rn(f, bias_f);
           if (p.relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
-          reinterpret_cast<float *>(p.out)[idx] = f;
+          if (p.n_peers > 0) {
+            for (int d = 0; d < p.n_peers; ++d) reinterpret_cast<float *>(p.peer_out[d])[idx] = f;
+          } else {
+            reinterpret_cast<float *>(p.out)[idx] = f;
+          }
           if (p.acc_dump) p.acc_dump[size_t(orow) * size_t(p.ld_dump) + size_t(ocol)] = int32_t(v[j]);
         } else if (p.out_kind == OUT_F32) {
           float f = __uint_as_float(v[j]);

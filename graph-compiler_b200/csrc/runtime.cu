@@ -2,6 +2,7 @@
 // planning and the small helper kernels (split-K reduction + epilogue, int8
 // column sums, exact-order SIMT matmul).
 #include "runtime.h"
+#include "tune_cache.h"
 
 #include <algorithm>
 #include <atomic>
@@ -130,6 +131,16 @@ bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes) {
 static int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); }
 
 MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count) {
+  // a configuration measured for exactly this shape beats the model; an explicit GC_B200_TILE beats both
+  MatmulConfig c{};
+  if (!std::getenv("GC_B200_TILE") && tune::lookup(tune::Key{M, N, K, dtype_bytes, out_bytes}, &c) && (!c.swapped || M <= 64)) {
+    if (c.grid <= 0 || c.grid > sm_count) c.grid = sm_count;
+    return c;
+  }
+  return model_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count);
+}
+
+MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count) {
   MatmulConfig c{};
   const int bk = 128 / dtype_bytes;
   const int k_blocks = ceil_div(K, bk);
@@ -346,8 +357,16 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   const CUtensorMap tmB = operand_tmap(p.b, tb, eb, pb, mn_b, a.K, pair ? p.BN / 2 : p.BN, kpb);
 
   if (a.n_peers > 0) {
-    if (a.out_kind != OUT_F32 || cfg.swapped || a.n_peers > 8 || (a.N % 4) != 0 || a.ld_out)
-      throw std::invalid_argument("peer push needs the f32-out row-major form, N % 4 == 0 and at most 8 peers");
+    // f32 partial planes ([planes][M][N], pitch N) or finished results (bf16 / dequantised f32 with their
+    // post-ops, any 16-byte aligned pitch): every store is a full 16-byte chunk
+    const int per16 = a.out_kind == OUT_BF16 ? 8 : 4;
+    const size_t pitch_b = size_t(a.ld_out ? a.ld_out : a.N) * (a.out_kind == OUT_BF16 ? 2 : 4);
+    // (the weight-stationary form stores single elements and has no such constraint; it takes finished results only)
+    if ((a.out_kind != OUT_F32 && a.out_kind != OUT_BF16 && a.out_kind != OUT_DEQUANT_F32) || a.n_peers > 8 || a.acc_dump ||
+        (cfg.swapped ? a.out_kind == OUT_F32 : ((a.N % per16) != 0 || (pitch_b % 16) != 0)))
+      throw std::invalid_argument("peer stores need whole 16-byte chunks per row and at most 8 peers");
+    if (a.out_kind != OUT_F32 && (a.peer_plane != 0 || a.peer_rows != 0))
+      throw std::invalid_argument("planes and row scatter exist for f32 partial sums only");
     cfg.splits = 1;
     p.splits = 1;
     if (a.peer_rows > 0 && (a.peer_rows * a.n_peers != a.M)) throw std::invalid_argument("row scatter needs M = peers x rows per peer");

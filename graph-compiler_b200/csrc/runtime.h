@@ -61,6 +61,8 @@ struct MatmulConfig {
 };
 // dtype_bytes: 2 (bf16) or 1 (int8).  out_bytes: bytes per output element written by the GEMM kernel.
 MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
+// The fitted time model alone (select_matmul_config consults the measured configurations of tune_cache.h first).
+MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
 // Whether the TMA path can take this operand layout (16-byte aligned base and row pitch).
 bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes);
 

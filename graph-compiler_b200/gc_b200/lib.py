@@ -57,11 +57,20 @@ def load() -> C.CDLL:
         "gcb200_matmul_bf16_f32out_push": [_vp, _vp, C.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp],
         "gcb200_reduce_bias_act_bf16": [_vp, _int, _i64, _vp, _vp, _i64, _i64, _int, _vp],
         "gcb200_matmul_bf16_f32out_scatter": [_vp, _vp, C.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp],
+        "gcb200_matmul_bf16_allgather": [_vp, _vp, _vp, C.POINTER(_vp), _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp],
+        "gcb200_matmul_u8s8_allgather": [_vp, _vp, _vp, _vp, _vp, C.POINTER(_vp), _int, _i64, _i64, _i64, _i64, _int, _vp],
         "gcb200_reduce_slice_broadcast_bf16": [_vp, _int, _i64, _i64, _vp, C.POINTER(_vp), _int, _i64, _int, _vp],
         "gcb200_matmul_u8s8": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp],
         "gcb200_colsum_s8": [_vp, _vp, _i64, _i64, _i32, _vp],
         "gcb200_matmul_f32": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp],
         "gcb200_select_matmul_config": [_i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig)],
+        "gcb200_model_matmul_config": [_i64, _i64, _i64, _int, _int, _int, C.POINTER(MatmulConfig)],
+        "gcb200_tune_cache_put": [_i64, _i64, _i64, _int, _int, C.POINTER(MatmulConfig)],
+        "gcb200_tune_cache_get": [_i64, _i64, _i64, _int, _int, C.POINTER(MatmulConfig), C.POINTER(_int)],
+        "gcb200_tune_cache_load": [C.c_char_p, C.POINTER(_int)],
+        "gcb200_tune_cache_save": [C.c_char_p, C.POINTER(_int)],
+        "gcb200_tune_cache_erase": [_i64, _i64, _i64, _int, _int],
+        "gcb200_tune_cache_clear": [],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -117,6 +126,44 @@ def select_matmul_config(M, N, K, dtype_bytes=2, out_bytes=2, sms=148) -> Matmul
     return cfg
 
 
+def model_matmul_config(M, N, K, dtype_bytes=2, out_bytes=2, sms=148) -> MatmulConfig:
+    """The time model's choice, ignoring measured configurations."""
+    cfg = MatmulConfig()
+    check(load().gcb200_model_matmul_config(M, N, K, dtype_bytes, out_bytes, sms, C.byref(cfg)))
+    return cfg
+
+
+def tune_cache_put(M, N, K, cfg: MatmulConfig, dtype_bytes=2, out_bytes=2):
+    check(load().gcb200_tune_cache_put(M, N, K, dtype_bytes, out_bytes, C.byref(cfg)))
+
+
+def tune_cache_get(M, N, K, dtype_bytes=2, out_bytes=2):
+    """The measured configuration recorded for this shape, or None."""
+    cfg, found = MatmulConfig(), _int(0)
+    check(load().gcb200_tune_cache_get(M, N, K, dtype_bytes, out_bytes, C.byref(cfg), C.byref(found)))
+    return cfg if found.value else None
+
+
+def tune_cache_load(path: str) -> int:
+    n = _int(0)
+    check(load().gcb200_tune_cache_load(os.fsencode(path), C.byref(n)))
+    return n.value
+
+
+def tune_cache_save(path: str) -> int:
+    n = _int(0)
+    check(load().gcb200_tune_cache_save(os.fsencode(path), C.byref(n)))
+    return n.value
+
+
+def tune_cache_erase(M, N, K, dtype_bytes=2, out_bytes=2):
+    check(load().gcb200_tune_cache_erase(M, N, K, dtype_bytes, out_bytes))
+
+
+def tune_cache_clear():
+    check(load().gcb200_tune_cache_clear())
+
+
 # ----------------------------------------------------------------------------- launchers on torch CUDA tensors
 def matmul_bf16(A, B, bias=None, relu=False, transpose_a=False, transpose_b=False, out=None, cfg: MatmulConfig | None = None):
     """Y = act(bf16(bf16(op(A).op(B)) + bias)) on bf16 CUDA tensors."""
@@ -163,6 +210,26 @@ def matmul_bf16_f32out_scatter(A, B, peer_ptrs, my_plane: int):
     N = B.shape[1]
     arr = (_vp * len(peer_ptrs))(*peer_ptrs)
     check(load().gcb200_matmul_bf16_f32out_scatter(_ptr(A), _ptr(B), arr, len(peer_ptrs), my_plane, M, N, K, _stream()))
+
+
+def matmul_bf16_allgather(A, B, bias, relu, peer_ptrs, ldc: int, transpose_a=False, transpose_b=False):
+    """This rank's column block act(A.B + bias) stored by the GEMM epilogue at ``peer_ptrs[d]`` (ints: address of
+    the block's first element inside rank d's [M, ldc] bf16 result) of every rank."""
+    M = A.shape[1] if transpose_a else A.shape[0]
+    K = A.shape[0] if transpose_a else A.shape[1]
+    N = B.shape[0] if transpose_b else B.shape[1]
+    arr = (_vp * len(peer_ptrs))(*peer_ptrs)
+    check(load().gcb200_matmul_bf16_allgather(_ptr(A), _ptr(B), _ptr(bias), arr, len(peer_ptrs), M, N, K, ldc,
+                                              int(transpose_a), int(transpose_b), int(relu), _stream()))
+
+
+def matmul_u8s8_allgather(A, W, scale, bias, comp, peer_ptrs, ldc: int, transpose_b=False):
+    """u8 x s8 column block, dequantised f32, stored at ``peer_ptrs[d]`` inside every rank's [M, ldc] f32 result."""
+    M, K = A.shape
+    N = W.shape[0] if transpose_b else W.shape[1]
+    arr = (_vp * len(peer_ptrs))(*peer_ptrs)
+    check(load().gcb200_matmul_u8s8_allgather(_ptr(A), _ptr(W), _ptr(scale), _ptr(bias), _ptr(comp), arr, len(peer_ptrs),
+                                              M, N, K, ldc, int(transpose_b), _stream()))
 
 
 def reduce_slice_broadcast_bf16(parts, bias, relu, out_ptrs, row0: int):

@@ -210,6 +210,56 @@ class ShardedGemm:
         return torch.cat(parts, dim=1)
 
 
+class PeerGatherGemm:
+    """Column-sharded GEMM with the all-gather fused into the GEMM: the epilogue stores every finished chunk of
+    this rank's column block into the same place of EVERY rank's full [M, N] result (peer-mapped symmetric
+    memory, plain NVLink stores that overlap the tiles still being computed); one cross-rank barrier and every
+    rank holds the whole C.  ``quant`` selects the u8 x s8 form (f32 result; scales, bias and zero-point
+    compensation split with the columns).  Two result buffers alternate, so a result stays valid until the
+    step after the next one.  Batches of at most 64 rows run the weight-stationary kernel, which stores its
+    elements to the peers one by one (the result is small)."""
+
+    def __init__(self, W_shard, M: int, N_total: int, device, bias_shard=None, relu: bool = False, quant=None, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import lib
+
+        self._lib = lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.W, self.bias, self.relu, self.quant = W_shard, bias_shard, relu, quant
+        self.N = N_total
+        n_shard = W_shard.shape[1]
+        if n_shard * self.world != N_total:
+            raise ValueError(f"{self.world} column blocks of {n_shard} do not make {N_total} columns")
+        dtype = torch.float32 if quant is not None else torch.bfloat16
+        esz = 4 if quant is not None else 2
+        if quant is not None:
+            scale, zp = quant
+            self.scale = scale
+            self.comp = lib.colsum_s8(W_shard, zp)    # zp * sum_k W[k, n]: per column, so it splits with N
+        self.bufs, self.hdls, self.ptrs = [], [], []
+        for _ in range(2):
+            t = symm.empty((M, N_total), dtype=dtype, device=device)
+            h = symm.rendezvous(t, self.group)
+            self.bufs.append(t)
+            self.hdls.append(h)
+            self.ptrs.append([int(p) + self.rank * n_shard * esz for p in h.buffer_ptrs])
+        self.turn = 0
+
+    def step(self, A):
+        i = self.turn
+        self.turn ^= 1
+        if self.quant is not None:
+            self._lib.matmul_u8s8_allgather(A, self.W, self.scale, self.bias, self.comp, self.ptrs[i], self.N)
+        else:
+            self._lib.matmul_bf16_allgather(A, self.W, self.bias, self.relu, self.ptrs[i], self.N)
+        self.hdls[i].barrier(channel=0)   # every rank's column block has landed here and is visible
+        return self.bufs[i]
+
+
 class ShardedQuantGemm:
     """u8 x s8 GEMM split along N: weights, scales, bias (and the zero-point compensation, which is a
     per-column sum over K) all split with the columns, so every rank's block is complete by itself."""

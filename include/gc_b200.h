@@ -92,6 +92,23 @@ int gcb200_matmul_bf16_f32out_scatter(const void *A, const void *B, void *const 
 int gcb200_reduce_slice_broadcast_bf16(const float *parts, int nparts, int64_t rows, int64_t N, const void *bias,
                                        void *const *peer_out, int n_peers, int64_t row0, int relu, void *stream);
 
+/* Column-sharded GEMM across GPUs with the all-gather of C done by the GEMM epilogue: this rank computes
+ * its column block  act(bf16(bf16(A . B_block) + bias_block))  ([M, N] with N = columns of the block) and
+ * stores every finished 16-byte chunk straight into EVERY rank's full result: peer_C[d] is the address of
+ * element (0, first column of this rank's block) inside rank d's [M, ldc] bf16 buffer (peer-mapped, this
+ * rank's own included).  Plain NVLink stores, no loads from a peer; after one cross-rank barrier every rank
+ * holds the whole C.  The across-device form of the reference's N split (NThreads,
+ * DeepTileContractionOp.cpp:562-601).  N must be a multiple of 8, ldc of 8 (no such limit for M <= 64, where
+ * the weight-stationary kernel stores single elements). */
+int gcb200_matmul_bf16_allgather(const void *A, const void *B, const void *bias, void *const *peer_C, int n_peers,
+                                 int64_t M, int64_t N, int64_t K, int64_t ldc, int transpose_a, int transpose_b, int relu,
+                                 void *stream);
+/* The u8 x s8 counterpart: out = float(acc - comp[n]) * scale[n] + bias[n] stored as f32 into every rank's
+ * [M, ldc] buffer at peer_C[d]; scales, bias and zero-point compensation are those of the column block. */
+int gcb200_matmul_u8s8_allgather(const void *A, const void *W, const float *scale, const float *bias, const int32_t *comp,
+                                 void *const *peer_C, int n_peers, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                                 int transpose_b, void *stream);
+
 /* Sum `nparts` f32 planes [M,N] (`plane_stride` elements apart) in plane order,
  * then apply the bf16 epilogue bf16(bf16(sum)+bias), ReLU.  The reduce + cast
  * step of the K-split form (DeepTileContractionOp.cpp:446-471). */
@@ -133,6 +150,22 @@ typedef struct {
 } gcb200_matmul_config;
 int gcb200_select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count,
                                 gcb200_matmul_config *cfg);
+
+/* Measured configurations.  A configuration recorded for a shape (found by timing candidates on the
+ * device, see gc_b200/tune.py) takes precedence over the model in gcb200_select_matmul_config and in every
+ * matmul launch of that exact shape; the cache is a text file (one "M N K dtype_bytes out_bytes : swapped bn
+ * splits stages group_m grid pair kpb" line per shape), read once from the path in GC_B200_TUNE_CACHE and
+ * loadable / savable explicitly.  The reference's counterpart is the per-op override attribute set of
+ * MatmulConfigAnalysis.cpp:368-401.  Host logic; needs no device. */
+int gcb200_tune_cache_put(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, const gcb200_matmul_config *cfg);
+int gcb200_tune_cache_get(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, gcb200_matmul_config *cfg, int *found);
+int gcb200_tune_cache_load(const char *path, int *entries_read);
+int gcb200_tune_cache_save(const char *path, int *entries_written);
+int gcb200_tune_cache_erase(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes);
+int gcb200_tune_cache_clear(void);
+/* The model's own choice, ignoring recorded configurations (what a tuner compares against). */
+int gcb200_model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count,
+                               gcb200_matmul_config *cfg);
 
 /* bf16 matmul with an explicit tile configuration (tuning, tests). */
 int gcb200_matmul_bf16_cfg(const void *A, const void *B, const void *bias, void *Y, int64_t M, int64_t N, int64_t K,

@@ -96,3 +96,90 @@ def test_tensor_parallel_mlp_on_gpus(mode):
     pre = np.abs(bf16_f32(want)) + np.abs(bf16_f32(_bits(Bs[3])))[None, :]
     mx, same = assert_bf16_close(res[0][0], want, max(HIDDEN), what=f"tp {mode}", floor_div=1.0, pre=pre)
     print(f"tp{world} {mode}: max_abs={mx:.4g} bit-identical={same:.5f}")
+
+
+def _gather_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    from gc_b200 import lib
+    from gc_b200.tensor_parallel import PeerGatherGemm, ShardedAttention, shard_range
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        A, B, bias, Aq, Wq, sc, bi, Q, K, V = _gather_inputs()
+        M, N = A.shape[0], B.shape[1]
+        lo, hi = shard_range(N, world, rank)
+        gg = PeerGatherGemm(B[:, lo:hi].contiguous().to(dev), M, N, dev, bias_shard=bias[lo:hi].contiguous().to(dev), relu=True)
+        gq = PeerGatherGemm(Wq[:, lo:hi].contiguous().to(dev), M, N, dev, bias_shard=bi[lo:hi].contiguous().to(dev),
+                            quant=(sc[lo:hi].contiguous().to(dev), 128))
+        gd = PeerGatherGemm(B[:, lo:hi].contiguous().to(dev), 16, N, dev, bias_shard=bias[lo:hi].contiguous().to(dev), relu=True)
+        dec = gd.step(A[:16].contiguous().to(dev))       # decode-shaped batch: the weight-stationary kernel stores to the peers
+        torch.cuda.synchronize()
+        dec = _bits(dec).copy()
+        outs = []
+        for _ in range(3):                     # repeated steps exercise the alternating result buffers
+            c = gg.step(A.to(dev))
+            cq = gq.step(Aq.to(dev))
+            torch.cuda.synchronize()
+            outs.append((_bits(c).copy(), cq.cpu().numpy().copy()))
+        o = ShardedAttention(world, rank).step(Q.to(dev), K.to(dev), V.to(dev), 128 ** -0.5, True, gather=True)
+        torch.cuda.synchronize()
+        assert lib.device_error() == 0
+        q.put((rank, outs, _bits(o).copy(), dec))
+    finally:
+        dist.destroy_process_group()
+
+
+def _gather_inputs():
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 256, 2048, 1024
+    A = (torch.rand(M, K, generator=g) * 2 - 1).bfloat16()
+    B = (torch.rand(K, N, generator=g) * 2 - 1).bfloat16()
+    bias = (torch.rand(N, generator=g) * 2 - 1).bfloat16()
+    Aq = torch.randint(0, 256, (M, K), generator=g, dtype=torch.uint8)
+    Wq = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8)
+    sc, bi = torch.rand(N, generator=g) * 0.009 + 0.001, torch.rand(N, generator=g) * 2 - 1
+    Q, Kt, V = (torch.randn(2, 4, 256, 128, generator=g).bfloat16() for _ in range(3))
+    return A, B, bias, Aq, Wq, sc, bi, Q, Kt, V
+
+
+def test_column_sharded_gemms_gathered_by_the_epilogue_and_head_sharded_attention():
+    """BASELINE's N-sharded GEMM sweep and int8 GEMM with the all-gather of C done by peer stores from the GEMM
+    epilogue, and attention sharded by (batch, head): every rank must end with the single-device result."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    if world == 3:
+        world = 2
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    res = {r: (outs, att, dec) for r, outs, att, dec in got}
+    A, B, bias, Aq, Wq, sc, bi, Q, K, V = _gather_inputs()
+    want, acc = oracle.linear_bf16(_bits(A), _bits(B), _bits(bias), relu=True, return_acc=True)
+    _, wantq = oracle.linear_u8s8(Aq.numpy(), Wq.numpy(), sc.numpy(), bi.numpy(), zp_a=128)
+    for r in range(world):
+        for step in range(3):
+            assert np.array_equal(res[r][0][step][0], res[0][0][0][0]), (r, step)
+            assert np.array_equal(res[r][0][step][1], wantq), (r, step)       # int8: exact sums, same two f32 operations
+        assert np.array_equal(res[r][1], res[0][1])
+        assert np.array_equal(res[r][2], res[0][2])
+    mx, same = assert_bf16_close(res[0][0][0][0], want, A.shape[1], what="gathered gemm", pre=acc)
+    assert_bf16_close(res[0][2], want[:16], A.shape[1], what="gathered decode-shaped gemm", pre=acc[:16])
+    from gc_b200 import lib
+    dev = torch.device("cuda", 0)
+    single = lib.attention_bf16(Q.to(dev), K.to(dev), V.to(dev), 128 ** -0.5, True)
+    assert np.array_equal(res[0][1], _bits(single))     # heads are independent: sharding changes no bit
+    print(f"gathered gemm on {world} GPUs: max_abs={mx:.4g} bit-identical={same:.5f}")
