@@ -185,8 +185,10 @@ def test_tile_selection_for_the_benchmark_shapes():
     assert (c.bn, c.kpb, c.splits) == (128, 2, 1)
     c = sel(128, 256, 512)              # BASELINE configs[0]
     assert c.swapped == 0 and c.bn in (64, 128, 256)
-    c = sel(1024, 4096, 4096, 1, 4)     # int8
-    assert c.swapped == 0 and c.bn % 32 == 0
+    c = sel(1024, 4096, 4096, 1, 4)     # int8, less than a wave of 256-wide tiles: 128-wide, two K blocks per stage
+    assert c.swapped == 0 and (c.bn, c.kpb, c.splits, c.grid) == (128, 2, 1, 148)
+    c = sel(8192, 8192, 8192, 1, 4)     # int8, many waves: 256-wide tiles
+    assert (c.bn, c.kpb, c.splits) == (256, 1, 1)
     for M, N, K in [(1, 1, 1), (5, 7, 9), (200, 328, 136), (64, 128, 64), (65, 100000, 64)]:
         c = sel(M, N, K)
         assert 16 <= c.bn <= 256 and c.bn % 16 == 0 and 2 <= c.stages <= 8 and c.splits >= 1 and c.grid >= 1
