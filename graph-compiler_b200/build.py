@@ -61,11 +61,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if r.returncode != 0:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
     if jobs or force or not os.path.exists(LIB):
-        link = [NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-cudart", "static", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"]
+        # link beside the target and rename: a reader (a running process, a copy of the tree) never sees a partial file
+        tmp = LIB + ".tmp"
+        link = [NVCC, *ARCH, "-shared", "-o", tmp, *objs, "-cudart", "static", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"]
         r = subprocess.run(link, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -181,10 +181,10 @@ MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byte
         if (us < best_t - 1e-9) { best_t = us; best_bn = bn_eff; best_sp = sp; best_kpb = kpb; }
       }
     }
-    // int8 MMAs take half the tensor cycles of bf16 ones, so with one K block per stage the stage hand-shake
-    // is what a CTA waits for; when 256-wide tiles do not even fill one wave, 128-wide tiles with two K
-    // blocks per stage use every SM and halve the hand-shakes per byte (measured with the tuner at
-    // 1024 x 4096 x 4096, operands from HBM: 30.8 us against 37.0 us; at 8192^3 256-wide tiles stay ahead).
+    // int8, less than one wave of 256-wide tiles: 128-wide tiles with two K blocks per stage give twice the
+    // tiles (every SM works, the tail wave is short) at the same hand-shakes per byte.  Measured with the
+    // tuner at 1024 x 4096 x 4096 with operands coming from HBM: 30.8 us against 37.0 us; the model's
+    // constants, fitted on bf16 shapes, rank the two the other way round.  At 8192^3 256-wide tiles stay ahead.
     if (dtype_bytes == 1 && best_bn == 256 && best_sp == 1 && k_blocks >= 4 && N % 128 == 0 &&
         ceil_div(M, 128) * ceil_div(N, 256) <= sm_count) {
       best_bn = 128;
