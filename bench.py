@@ -486,7 +486,10 @@ def main():
         exchange, why = None, ""
         # fused GEMM-epilogue exchanges: with two ranks sending the whole tile to the one peer is already minimal;
         # beyond that the partial sums are reduce-scattered by rows and the result all-gathered
-        want = os.environ.get("GC_B200_EXCHANGE", "peer_push")
+        # every partial sum to every rank costs (g - 1) x 8 MiB of NVLink stores per rank and exchange: best at two ranks
+        # (211 us per step against 228); the reduce-scatter form moves an all-reduce's traffic and wins beyond
+        # (8 ranks: 148 us against 289)
+        want = os.environ.get("GC_B200_EXCHANGE", "peer_push" if world <= 2 else "peer_reduce_scatter")
         if want in ("peer_push", "peer_reduce_scatter"):
             try:
                 exchange = (PeerPushExchange if want == "peer_push" else PeerReduceScatterExchange)(BATCH, HIDDEN[-1], dev)
