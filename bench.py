@@ -319,7 +319,8 @@ def run_sharded_case(spec: str, steps: int, warmup: int, rank: int, world: int):
     g = torch.Generator(device=dev).manual_seed(0)          # same seed on every rank: replicated inputs are identical
     f = spec.split(":")
     kind = f[0]
-    fused = os.environ.get("GC_B200_GATHER", "peer") != "nccl"
+    gather = os.environ.get("GC_B200_GATHER", "peer")
+    fused, mcast = gather != "nccl", gather == "multicast"
     how = "n/a"
     if kind in ("gemm", "decode"):
         M, N, K = (16, 28672, 8192) if kind == "decode" else map(int, f[1:4])
@@ -327,8 +328,9 @@ def run_sharded_case(spec: str, steps: int, warmup: int, rank: int, world: int):
         A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).bfloat16()
         Bs = (torch.rand((K, N), generator=g, device=dev) * 2 - 1).bfloat16()[:, lo:hi].contiguous()
         if fused:
-            op = PeerGatherGemm(Bs, M, N, dev)
-            fn, how = (lambda: op.step(A)), "all-gather of C by peer stores from the GEMM epilogue + one barrier"
+            op = PeerGatherGemm(Bs, M, N, dev, multicast=mcast)
+            fn, how = (lambda: op.step(A)), ("all-gather of C by multimem stores from the GEMM epilogue (NVSwitch multicast) + one barrier"
+                                             if op.multicast else "all-gather of C by peer stores from the GEMM epilogue + one barrier")
         else:
             op = ShardedGemm(Bs, world, rank)
             fn, how = (lambda: op.step(A, gather=True)), "NCCL all-gather of C"
@@ -341,8 +343,9 @@ def run_sharded_case(spec: str, steps: int, warmup: int, rank: int, world: int):
         sc = (torch.rand(N, generator=g, device=dev) * 0.009 + 0.001)[lo:hi].contiguous()
         bi = (torch.rand(N, generator=g, device=dev) * 2 - 1)[lo:hi].contiguous()
         if fused:
-            op = PeerGatherGemm(W, M, N, dev, bias_shard=bi, quant=(sc, 128))
-            fn, how = (lambda: op.step(A)), "all-gather of C by peer stores from the GEMM epilogue + one barrier"
+            op = PeerGatherGemm(W, M, N, dev, bias_shard=bi, quant=(sc, 128), multicast=mcast)
+            fn, how = (lambda: op.step(A)), ("all-gather of C by multimem stores from the GEMM epilogue (NVSwitch multicast) + one barrier"
+                                             if op.multicast else "all-gather of C by peer stores from the GEMM epilogue + one barrier")
         else:
             op = ShardedQuantGemm(W, sc, bi, 128, world, rank)
             fn, how = (lambda: op.step(A, gather=True)), "NCCL all-gather of C"
@@ -490,9 +493,12 @@ def main():
         # (211 us per step against 228); the reduce-scatter form moves an all-reduce's traffic and wins beyond
         # (8 ranks: 148 us against 289)
         want = os.environ.get("GC_B200_EXCHANGE", "peer_push" if world <= 2 else "peer_reduce_scatter")
-        if want in ("peer_push", "peer_reduce_scatter"):
+        if want in ("peer_push", "peer_push_multicast", "peer_reduce_scatter"):
             try:
-                exchange = (PeerPushExchange if want == "peer_push" else PeerReduceScatterExchange)(BATCH, HIDDEN[-1], dev)
+                if want == "peer_reduce_scatter":
+                    exchange = PeerReduceScatterExchange(BATCH, HIDDEN[-1], dev)
+                else:
+                    exchange = PeerPushExchange(BATCH, HIDDEN[-1], dev, multicast=(want == "peer_push_multicast"))
             except Exception as e:   # symmetric memory unavailable: NCCL all-reduce baseline
                 why = f" (fused exchange unavailable: {type(e).__name__})"
         if exchange is None:
@@ -549,6 +555,8 @@ def main():
 
         parallelism = (f"tp{world}: layers 1,3 column-parallel, layers 2,4 row-parallel, f32 partial sums exchanged by "
                        + {"peer_push": "GEMM-epilogue peer stores over NVLink (every rank receives every partial sum) + local reduce",
+                          "peer_push_multicast": "GEMM-epilogue multimem stores (one NVLink crossing per chunk, the NVSwitch writes every "
+                                                 "rank's copy) + local reduce",
                           "peer_reduce_scatter": "GEMM-epilogue peer stores over NVLink to the row owner (reduce-scatter), owner reduces "
                                                  "and stores the bf16 rows to every rank (all-gather)",
                           "all_reduce": "NCCL all-reduce"}[exchange.name] + ("; one CUDA-graph replay per step" if graph is not None else "") + why)

@@ -149,6 +149,57 @@ GCB_EXPORT int gcb200_matmul_bf16_f32out_push(const void *A, const void *B, void
   });
 }
 
+// The three peer-store forms with ONE multicast address instead of a list of peer addresses (see the header).
+GCB_EXPORT int gcb200_matmul_bf16_f32out_push_mc(const void *A, const void *B, void *mc_buf, int my_plane, int64_t M, int64_t N,
+                                                 int64_t K, void *stream) {
+  return guarded([&] {
+    require(A && B && mc_buf && my_plane >= 0 && (reinterpret_cast<uintptr_t>(mc_buf) & 15) == 0, "bad arguments");
+    require(M > 64 && N > 0 && K > 0, "multicast push needs M > 64 and positive N, K");
+    if (!(tma_compatible(A, K, 2) && tma_compatible(B, N, 2))) throw std::logic_error("push matmul needs 16-byte aligned operand rows");
+    void *const one[1] = {mc_buf};
+    MatmulArgs a;
+    a.A = A; a.B = B; a.M = M; a.N = N; a.K = K;
+    a.out_kind = OUT_F32; a.out = mc_buf;
+    a.n_peers = 1; a.peer_plane = my_plane; a.peer_out = one; a.peer_multicast = 1;
+    matmul_tc(a, static_cast<cudaStream_t>(stream));
+  });
+}
+
+GCB_EXPORT int gcb200_matmul_bf16_allgather_mc(const void *A, const void *B, const void *bias, void *mc_C, int64_t M, int64_t N,
+                                               int64_t K, int64_t ldc, int transpose_a, int transpose_b, int relu, void *stream) {
+  return guarded([&] {
+    require(A && B && mc_C && (reinterpret_cast<uintptr_t>(mc_C) & 15) == 0, "bad arguments");
+    require(M > 64 && N > 0 && K > 0 && ldc >= N, "multicast all-gather matmul needs M > 64, positive N, K and ldc >= N");
+    if (!(tma_compatible(A, transpose_a ? M : K, 2) && tma_compatible(B, transpose_b ? K : N, 2)))
+      throw std::logic_error("all-gather matmul needs 16-byte aligned operand rows");
+    void *const one[1] = {mc_C};
+    MatmulArgs a;
+    a.A = A; a.B = B; a.M = M; a.N = N; a.K = K; a.trans_a = transpose_a; a.trans_b = transpose_b;
+    a.out_kind = OUT_BF16; a.out = mc_C; a.ld_out = ldc;
+    a.bias_kind = bias ? BIAS_BF16 : BIAS_NONE; a.bias = bias; a.relu = relu;
+    a.n_peers = 1; a.peer_out = one; a.peer_multicast = 1;
+    matmul_tc(a, static_cast<cudaStream_t>(stream));
+  });
+}
+
+GCB_EXPORT int gcb200_matmul_u8s8_allgather_mc(const void *A, const void *W, const float *scale, const float *bias,
+                                               const int32_t *comp, void *mc_C, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                                               int transpose_b, void *stream) {
+  return guarded([&] {
+    require(A && W && scale && mc_C && (reinterpret_cast<uintptr_t>(mc_C) & 15) == 0, "bad arguments");
+    require(M > 64 && N > 0 && K > 0 && ldc >= N, "multicast all-gather matmul needs M > 64, positive N, K and ldc >= N");
+    if (!(tma_compatible(A, K, 1) && tma_compatible(W, transpose_b ? K : N, 1)))
+      throw std::logic_error("int8 matmul needs K and N to be multiples of 16 and 16-byte aligned bases");
+    void *const one[1] = {mc_C};
+    MatmulArgs a;
+    a.A = A; a.B = W; a.M = M; a.N = N; a.K = K; a.int8 = 1; a.trans_b = transpose_b;
+    a.out_kind = OUT_DEQUANT_F32; a.out = mc_C; a.ld_out = ldc; a.scale = scale; a.comp = comp;
+    a.bias_kind = bias ? BIAS_F32 : BIAS_NONE; a.bias = bias;
+    a.n_peers = 1; a.peer_out = one; a.peer_multicast = 1;
+    matmul_tc(a, static_cast<cudaStream_t>(stream));
+  });
+}
+
 GCB_EXPORT int gcb200_matmul_bf16_f32out_scatter(const void *A, const void *B, void *const *peer_bufs, int n_peers, int my_plane,
                                                  int64_t M, int64_t N, int64_t K, void *stream) {
   return guarded([&] {

@@ -143,7 +143,9 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
             *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[owner]) + off) = val;
           } else {
             const size_t off = (size_t(p.peer_plane) * size_t(p.out_rows) + size_t(grow)) * ld_b + size_t(gcol) * esz;
-            for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[d]) + off) = val;
+            if (p.peer_multicast) multimem_st_16(reinterpret_cast<uint8_t *>(p.peer_out[0]) + off, val);
+            else
+              for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[d]) + off) = val;
           }
         } else if (vec_ok && nvalid == cpc) {
           *reinterpret_cast<uint4 *>(g) = val;

@@ -67,6 +67,7 @@ struct GemmParams {
   int n_peers, peer_plane;
   int peer_rows;        // 0: every peer receives the whole tile; > 0: rows [d * peer_rows, (d + 1) * peer_rows) go to
                         // peer d only, whose buffer is [planes][peer_rows][ld_out] (reduce-scatter by rows)
+  int peer_multicast;   // 1: peer_out[0] is a multicast address covering every rank's buffer; one multimem store per chunk
   void *peer_out[8];
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
   // TMA-store epilogue (one-CTA kernel, row-major orientation): tmC covers the output as

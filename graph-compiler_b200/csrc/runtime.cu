@@ -379,6 +379,9 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
     cfg.splits = 1;
     p.splits = 1;
     if (a.peer_rows > 0 && (a.peer_rows * a.n_peers != a.M)) throw std::invalid_argument("row scatter needs M = peers x rows per peer");
+    if (a.peer_multicast && (a.n_peers != 1 || a.peer_rows != 0 || cfg.swapped))
+      throw std::invalid_argument("multicast stores take one address, every rank receives everything, row-major form only");
+    p.peer_multicast = a.peer_multicast;
     p.n_peers = a.n_peers;
     p.peer_plane = a.peer_plane;
     p.peer_rows = a.peer_rows;

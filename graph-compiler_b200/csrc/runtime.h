@@ -95,6 +95,7 @@ struct MatmulArgs {
   int peer_plane = 0;
   int peer_rows = 0;            // > 0: rows are scattered to their owner (row / peer_rows) instead of sent to every peer
   void *const *peer_out = nullptr;
+  int peer_multicast = 0;       // 1: n_peers == 1 and peer_out[0] is an NVLink multicast address of all ranks' buffers
   const MatmulConfig *force = nullptr; // optional override
   void *scratch = nullptr;      // optional caller-provided split-K scratch (else the device workspace)
   size_t scratch_bytes = 0;

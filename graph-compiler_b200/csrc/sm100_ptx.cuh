@@ -332,6 +332,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// One 16-byte store to a multicast address: the NVSwitch writes the same bytes at this offset of every
+// GPU's buffer bound to the multicast object (one NVLink crossing per store instead of one per peer).
+// The value is copied as is, whatever its element type.
+__device__ __forceinline__ void multimem_st_16(void *mc_addr, uint4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               :: "l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                  "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // cvt.rn.bf16x2 returns 0x7FFF for a NaN input; the reference conversion returns 0x7FC0
 // (BrgemmInterface.h:83-92).  Patch the (rare) NaN halves of a packed pair.
 __device__ __forceinline__ uint32_t bf16x2_fix_nan(uint32_t w) {

@@ -57,6 +57,9 @@ def load() -> C.CDLL:
         "gcb200_matmul_bf16_f32out_push": [_vp, _vp, C.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp],
         "gcb200_reduce_bias_act_bf16": [_vp, _int, _i64, _vp, _vp, _i64, _i64, _int, _vp],
         "gcb200_matmul_bf16_f32out_scatter": [_vp, _vp, C.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp],
+        "gcb200_matmul_bf16_f32out_push_mc": [_vp, _vp, _vp, _int, _i64, _i64, _i64, _vp],
+        "gcb200_matmul_bf16_allgather_mc": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _int, _vp],
+        "gcb200_matmul_u8s8_allgather_mc": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp],
         "gcb200_matmul_bf16_allgather": [_vp, _vp, _vp, C.POINTER(_vp), _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp],
         "gcb200_matmul_u8s8_allgather": [_vp, _vp, _vp, _vp, _vp, C.POINTER(_vp), _int, _i64, _i64, _i64, _i64, _int, _vp],
         "gcb200_reduce_slice_broadcast_bf16": [_vp, _int, _i64, _i64, _vp, C.POINTER(_vp), _int, _i64, _int, _vp],
@@ -202,6 +205,28 @@ def matmul_bf16_f32out_push(A, B, peer_ptrs, my_plane: int):
     N = B.shape[1]
     arr = (_vp * len(peer_ptrs))(*peer_ptrs)
     check(load().gcb200_matmul_bf16_f32out_push(_ptr(A), _ptr(B), arr, len(peer_ptrs), my_plane, M, N, K, _stream()))
+
+
+def matmul_bf16_f32out_push_mc(A, B, mc_ptr: int, my_plane: int):
+    """f32 partial sums of A.B stored once, through the multicast address ``mc_ptr``, into plane ``my_plane`` of every rank's buffer."""
+    M, K = A.shape
+    N = B.shape[1]
+    check(load().gcb200_matmul_bf16_f32out_push_mc(_ptr(A), _ptr(B), _vp(mc_ptr), my_plane, M, N, K, _stream()))
+
+
+def matmul_bf16_allgather_mc(A, B, bias, relu, mc_ptr: int, ldc: int):
+    """This rank's column block stored through the multicast address ``mc_ptr`` (the block's first element inside the
+    multicast mapping of the [M, ldc] result) into every rank's result."""
+    M, K = A.shape
+    N = B.shape[1]
+    check(load().gcb200_matmul_bf16_allgather_mc(_ptr(A), _ptr(B), _ptr(bias), _vp(mc_ptr), M, N, K, ldc, 0, 0, int(relu), _stream()))
+
+
+def matmul_u8s8_allgather_mc(A, W, scale, bias, comp, mc_ptr: int, ldc: int):
+    M, K = A.shape
+    N = W.shape[1]
+    check(load().gcb200_matmul_u8s8_allgather_mc(_ptr(A), _ptr(W), _ptr(scale), _ptr(bias), _ptr(comp), _vp(mc_ptr), M, N, K, ldc,
+                                                 0, _stream()))
 
 
 def matmul_bf16_f32out_scatter(A, B, peer_ptrs, my_plane: int):

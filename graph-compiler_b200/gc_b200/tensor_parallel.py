@@ -64,6 +64,14 @@ class CudaOps:
         return self._lib.reduce_bias_act_bf16(planes, b, relu=relu)
 
 
+def _multicast_ptr(handle) -> int:
+    """The NVLink multicast address of a symmetric-memory allocation, or 0 when the allocation has none."""
+    try:
+        return int(getattr(handle, "multicast_ptr", 0) or 0)
+    except Exception:
+        return 0
+
+
 class AllReduceExchange:
     """Baseline exchange: local f32 partial sums, one NCCL/gloo all-reduce, then the epilogue on every rank."""
 
@@ -92,7 +100,7 @@ class PeerPushExchange:
     name = "peer_push"
     launches_per_pair = 3
 
-    def __init__(self, M: int, N: int, device, group=None):
+    def __init__(self, M: int, N: int, device, group=None, multicast: bool = False):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
@@ -102,19 +110,28 @@ class PeerPushExchange:
         self._lib = lib
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        self.bufs, self.hdls, self.ptrs = [], [], []
+        self.bufs, self.hdls, self.ptrs, self.mc = [], [], [], []
         for _ in range(2):
             t = symm.empty((self.world, M, N), dtype=torch.float32, device=device)
             h = symm.rendezvous(t, self.group)
             self.bufs.append(t)
             self.hdls.append(h)
             self.ptrs.append([int(p) for p in h.buffer_ptrs])
+            self.mc.append(_multicast_ptr(h) if multicast else 0)
+        # one multimem store per chunk through the NVSwitch instead of one store per peer (needs multicast-capable
+        # symmetric memory and the row-major kernel, M > 64)
+        self.multicast = bool(multicast and all(self.mc) and M > 64)
+        if self.multicast:
+            self.name = "peer_push_multicast"
         self.turn = 0
 
     def row_parallel(self, x, w, bias, relu):
         i = self.turn
         self.turn ^= 1
-        self._lib.matmul_bf16_f32out_push(x, w, self.ptrs[i], self.rank)
+        if self.multicast:
+            self._lib.matmul_bf16_f32out_push_mc(x, w, self.mc[i], self.rank)
+        else:
+            self._lib.matmul_bf16_f32out_push(x, w, self.ptrs[i], self.rank)
         self.hdls[i].barrier(channel=0)   # every rank's stores have landed and are visible
         return self._lib.reduce_bias_act_bf16(self.bufs[i], bias, relu=relu)
 
@@ -219,7 +236,8 @@ class PeerGatherGemm:
     step after the next one.  Batches of at most 64 rows run the weight-stationary kernel, which stores its
     elements to the peers one by one (the result is small)."""
 
-    def __init__(self, W_shard, M: int, N_total: int, device, bias_shard=None, relu: bool = False, quant=None, group=None):
+    def __init__(self, W_shard, M: int, N_total: int, device, bias_shard=None, relu: bool = False, quant=None, group=None,
+                 multicast: bool = False):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
@@ -240,19 +258,27 @@ class PeerGatherGemm:
             scale, zp = quant
             self.scale = scale
             self.comp = lib.colsum_s8(W_shard, zp)    # zp * sum_k W[k, n]: per column, so it splits with N
-        self.bufs, self.hdls, self.ptrs = [], [], []
+        self.bufs, self.hdls, self.ptrs, self.mc = [], [], [], []
         for _ in range(2):
             t = symm.empty((M, N_total), dtype=dtype, device=device)
             h = symm.rendezvous(t, self.group)
             self.bufs.append(t)
             self.hdls.append(h)
             self.ptrs.append([int(p) + self.rank * n_shard * esz for p in h.buffer_ptrs])
+            mc = _multicast_ptr(h) if multicast else 0
+            self.mc.append(mc + self.rank * n_shard * esz if mc else 0)
+        # multicast: each chunk leaves this GPU once and the NVSwitch writes it into every rank's result
+        self.multicast = bool(multicast and all(self.mc) and M > 64)
         self.turn = 0
 
     def step(self, A):
         i = self.turn
         self.turn ^= 1
-        if self.quant is not None:
+        if self.multicast and self.quant is not None:
+            self._lib.matmul_u8s8_allgather_mc(A, self.W, self.scale, self.bias, self.comp, self.mc[i], self.N)
+        elif self.multicast:
+            self._lib.matmul_bf16_allgather_mc(A, self.W, self.bias, self.relu, self.mc[i], self.N)
+        elif self.quant is not None:
             self._lib.matmul_u8s8_allgather(A, self.W, self.scale, self.bias, self.comp, self.ptrs[i], self.N)
         else:
             self._lib.matmul_bf16_allgather(A, self.W, self.bias, self.relu, self.ptrs[i], self.N)

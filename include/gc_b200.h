@@ -109,6 +109,19 @@ int gcb200_matmul_u8s8_allgather(const void *A, const void *W, const float *scal
                                  void *const *peer_C, int n_peers, int64_t M, int64_t N, int64_t K, int64_t ldc,
                                  int transpose_b, void *stream);
 
+/* The same three peer-store forms with ONE NVLink multicast address instead of a list of peer addresses:
+ * `mc_buf` / `mc_C` is the multicast mapping of a buffer that every rank has bound to the same multicast
+ * object (e.g. the multicast pointer of a torch symmetric-memory allocation), so each finished 16-byte chunk
+ * leaves this GPU once (`multimem.st`) and the NVSwitch writes it into every rank's copy, this rank's own
+ * included — 1/(g-1) of the NVLink traffic of the address-list forms.  Row-major kernel only (M > 64).
+ * mc_C points at this rank's column block inside the multicast mapping of the full [M, ldc] result. */
+int gcb200_matmul_bf16_f32out_push_mc(const void *A, const void *B, void *mc_buf, int my_plane, int64_t M, int64_t N,
+                                      int64_t K, void *stream);
+int gcb200_matmul_bf16_allgather_mc(const void *A, const void *B, const void *bias, void *mc_C, int64_t M, int64_t N,
+                                    int64_t K, int64_t ldc, int transpose_a, int transpose_b, int relu, void *stream);
+int gcb200_matmul_u8s8_allgather_mc(const void *A, const void *W, const float *scale, const float *bias, const int32_t *comp,
+                                    void *mc_C, int64_t M, int64_t N, int64_t K, int64_t ldc, int transpose_b, void *stream);
+
 /* Sum `nparts` f32 planes [M,N] (`plane_stride` elements apart) in plane order,
  * then apply the bf16 epilogue bf16(bf16(sum)+bias), ReLU.  The reduce + cast
  * step of the K-split form (DeepTileContractionOp.cpp:446-471). */

@@ -44,10 +44,16 @@ def _worker(rank, world, port, mode, q):
     try:
         X, Ws, Bs = _make()
         ws, bs = shard_weights([w.to(dev) for w in Ws], [b.to(dev) for b in Bs], world, rank)
-        fused = {"peer_push": PeerPushExchange, "peer_reduce_scatter": PeerReduceScatterExchange}.get(mode)
+        if mode == "peer_push_multicast":
+            fused = lambda m, n, d: PeerPushExchange(m, n, d, multicast=True)
+        else:
+            fused = {"peer_push": PeerPushExchange, "peer_reduce_scatter": PeerReduceScatterExchange}.get(mode)
         ex = fused(BATCH, HIDDEN[2], dev) if fused else AllReduceExchange(CudaOps())
         # the two row-parallel layers have different widths: one exchange object per width
         ex2 = fused(BATCH, HIDDEN[4], dev) if fused else ex
+        if mode == "peer_push_multicast" and not (ex.multicast and ex2.multicast):
+            q.put((rank, None))              # symmetric memory without a multicast mapping on this machine
+            return
         tp1 = TensorParallelMLP(ws[:2], bs[:2], relu=True, exchange=ex)
         tp2 = TensorParallelMLP(ws[2:], bs[2:], relu=True, exchange=ex2)
         outs = []
@@ -67,7 +73,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("mode", ["all_reduce", "peer_push", "peer_reduce_scatter"])
+@pytest.mark.parametrize("mode", ["all_reduce", "peer_push", "peer_reduce_scatter", "peer_push_multicast"])
 def test_tensor_parallel_mlp_on_gpus(mode):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
@@ -86,6 +92,8 @@ def test_tensor_parallel_mlp_on_gpus(mode):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+    if any(v is None for v in res.values()):
+        pytest.skip("no NVLink multicast mapping for symmetric memory here")
     X, Ws, Bs = _make()
     want = oracle.mlp_bf16(_bits(X), [_bits(w) for w in Ws], [_bits(b) for b in Bs], relu=True)
     for r in range(world):
@@ -125,6 +133,18 @@ def _gather_worker(rank, world, port, q):
             cq = gq.step(Aq.to(dev))
             torch.cuda.synchronize()
             outs.append((_bits(c).copy(), cq.cpu().numpy().copy()))
+        # the same two GEMMs with one multimem store per chunk (NVSwitch multicast), where symmetric memory offers it
+        mg = PeerGatherGemm(B[:, lo:hi].contiguous().to(dev), M, N, dev, bias_shard=bias[lo:hi].contiguous().to(dev), relu=True,
+                            multicast=True)
+        mq = PeerGatherGemm(Wq[:, lo:hi].contiguous().to(dev), M, N, dev, bias_shard=bi[lo:hi].contiguous().to(dev),
+                            quant=(sc[lo:hi].contiguous().to(dev), 128), multicast=True)
+        if mg.multicast and mq.multicast:
+            for _ in range(2):
+                c = mg.step(A.to(dev))
+                cq = mq.step(Aq.to(dev))
+                torch.cuda.synchronize()
+                assert np.array_equal(_bits(c), outs[0][0]), "multicast gather differs from the peer-store gather"
+                assert np.array_equal(cq.cpu().numpy(), outs[0][1])
         o = ShardedAttention(world, rank).step(Q.to(dev), K.to(dev), V.to(dev), 128 ** -0.5, True, gather=True)
         torch.cuda.synchronize()
         assert lib.device_error() == 0
