@@ -54,8 +54,61 @@ def measured_peaks():
 
 
 # --------------------------------------------------------------------------------------- clocks
+class NvmlClockSampler:
+    """SM clock and clock-event reasons read through NVML about once per millisecond while the timed region runs
+    (the region is ~13 ms long at the default step count: nvidia-smi's 200 ms loop would see it once at best).
+    Read-only queries; nothing on the GPU is changed."""
+
+    def __init__(self, gpu_index: int):
+        import pynvml
+
+        self.nv = pynvml
+        pynvml.nvmlInit()
+        self.h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        self.samples, self.stop_flag, self.t = [], False, None
+
+    def start(self):
+        nv = self.nv
+
+        def loop():
+            while not self.stop_flag:
+                try:
+                    self.samples.append((nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM),
+                                         nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)))
+                except Exception:
+                    pass
+                time.sleep(0.001)
+
+        self.t = threading.Thread(target=loop, daemon=True)
+        self.t.start()
+
+    def stop(self):
+        nv = self.nv
+        self.stop_flag = True
+        self.t.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        reasons = sorted(n for n, bit in names.items() if any(r & bit for _, r in self.samples))
+        try:
+            mx = float(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM))
+        except Exception:
+            mx = None
+        return {"sm_mhz": statistics.median(float(c) for c, _ in self.samples), "sm_max_mhz": mx, "reasons": reasons,
+                "samples": len(self.samples), "how": "NVML, 1 ms period, inside the timed region"}
+
+
+def make_clock_sampler(gpu_index: int):
+    try:
+        return NvmlClockSampler(gpu_index)
+    except Exception:
+        return ClockSampler(gpu_index)
+
+
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs (used when NVML
+    cannot be loaded)."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -571,7 +624,7 @@ def main():
         for _ in range(warmup):
             fn()
         barrier()
-        sampler = ClockSampler(local_rank) if sample_clocks else None
+        sampler = make_clock_sampler(local_rank) if sample_clocks else None
         if sampler:
             sampler.start()
         l0 = lib.launch_count()
