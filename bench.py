@@ -544,7 +544,7 @@ def main():
         # beyond that the partial sums are reduce-scattered by rows and the result all-gathered
         # every partial sum to every rank costs (g - 1) x 8 MiB of NVLink stores per rank and exchange: best at two ranks
         # (211 us per step against 228); the reduce-scatter form moves an all-reduce's traffic and wins beyond
-        # (8 ranks: 148 us against 289)
+        # (4 ranks: 171 us against 203; 8 ranks: 145 us against 289)
         want = os.environ.get("GC_B200_EXCHANGE", "peer_push" if world <= 2 else "peer_reduce_scatter")
         if want in ("peer_push", "peer_push_multicast", "peer_reduce_scatter"):
             try:
