@@ -1,7 +1,9 @@
-"""Tensor-parallel MLP on real GPUs (needs >= 2 devices; skipped otherwise): the two fused
-GEMM-epilogue peer-store exchanges (all-to-all and reduce-scatter + all-gather) and the NCCL
-all-reduce baseline against the oracle's single-device chain.  Ranks are child processes, one per GPU; NVLS is switched off and the
-kernels use plain peer stores, so a rank that fails cannot fault its peers' GPUs."""
+"""Multi-GPU paths on real GPUs (need >= 2 devices; skipped otherwise).  The tensor-parallel MLP with its exchanges
+fused into the GEMM epilogue (peer stores to every rank, reduce-scatter + all-gather, one multimem store per chunk through
+the NVSwitch multicast mapping) and with the NCCL all-reduce baseline, against the oracle's single-device chain; the
+column-sharded bf16 / int8 GEMMs whose all-gather is done by the epilogue, and head-sharded attention.  Ranks are child
+processes, one per GPU, NCCL's own NVLS off.  No rank is made to fail here: failure handling is tested on the host
+(tests/test_capi_host.py), so no rank leaves while its memory is bound to a multicast object."""
 import os
 import socket
 
