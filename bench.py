@@ -96,7 +96,7 @@ class NvmlClockSampler:
         except Exception:
             mx = None
         return {"sm_mhz": statistics.median(float(c) for c, _ in self.samples), "sm_max_mhz": mx, "reasons": reasons,
-                "samples": len(self.samples), "how": "NVML, 1 ms period, inside the timed region"}
+                "samples": len(self.samples), "how": "NVML, 1 ms period, from the start of the device-timed region to the end of the end-to-end region"}
 
 
 def make_clock_sampler(gpu_index: int):
@@ -639,15 +639,16 @@ def main():
         if world > 1:   # kernels launched by graph replays are not seen by the library's host-side counter
             launches += (holder.get("replays", 0) - r0) * holder.get("launches_per_replay", 0)
         ms = st.elapsed_time(en)
-        clocks = sampler.stop() if sampler else None
+        clocks = sampler   # still running: it also covers the end-to-end region that follows and is stopped there
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms / steps, launches, clocks
 
-    ms_dev, launches, clocks = timed(step_device, a.steps, a.warmup, sample_clocks=True)
+    ms_dev, launches, sampler = timed(step_device, a.steps, a.warmup, sample_clocks=True)
     ms_e2e, _, _ = timed(step_e2e, max(3, a.steps // 2), a.warmup)
+    clocks = sampler.stop()   # sampled from the start of the device-timed region to the end of the end-to-end one
     assert lib.device_error() == 0, "a kernel reported a bounded-wait time-out"
 
     peaks = measured_peaks()
