@@ -223,7 +223,7 @@ def cpu_onednn_class(rows=BATCH):
 
 
 # --------------------------------------------------------------------------------------- other BASELINE configs
-def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "auto"):
+def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "auto", library: bool = False):
     """Time one kernel-level case with device-resident inputs (CUDA events on the launching stream).
 
     spec: gemm:M:N:K | decode | int8:M:N:K | attention:B:H:S:D:causal(0|1) | cfg1 | llama2
@@ -296,6 +296,49 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "aut
     if flush_mode != "auto":
         l2_flush = flush_mode == "on"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if l2_flush else None
+
+    def time_fn(f, n):
+        if flush is None:
+            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            st.record()
+            for _ in range(n):
+                f()
+            en.record()
+            torch.cuda.synchronize()
+            return st.elapsed_time(en) / n
+        tot = 0.0   # small working set: write a buffer larger than L2 between timed launches
+        for _ in range(n):
+            flush.zero_()
+            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            st.record()
+            f()
+            en.record()
+            torch.cuda.synchronize()
+            tot += st.elapsed_time(en)
+        return tot / n
+
+    # Context only: the vendor library on the same tensors in the same run (cuBLAS through torch.matmul /
+    # torch._int_mm, the library attention through torch SDPA) - the same-box bar the kernels are held against.
+    lib_fn, lib_name = None, None
+    if library and kind in ("gemm", "decode", "cfg1"):
+        Yl = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        lib_fn, lib_name = (lambda: torch.matmul(A, B, out=Yl)), "cuBLAS bf16 via torch.matmul (no bias / ReLU)"
+    elif library and kind == "int8" and M > 16 and M % 8 == 0 and N % 8 == 0 and K % 8 == 0:
+        A8 = A.view(torch.int8)   # same bytes and work; torch._int_mm takes s8 x s8 only
+        lib_fn, lib_name = (lambda: torch._int_mm(A8, W)), "cuBLASLt s8 x s8 -> s32 via torch._int_mm (no dequantisation)"
+    elif library and kind == "attention":
+        import torch.nn.functional as F
+        lib_fn = lambda: F.scaled_dot_product_attention(Q, Kt, V, is_causal=bool(causal), scale=1.0 / math.sqrt(D))
+        lib_name = "torch scaled_dot_product_attention (library flash attention)"
+    lib_ms = None
+    if lib_fn is not None:
+        try:
+            for _ in range(3):
+                lib_fn()
+            torch.cuda.synchronize()
+            lib_ms = time_fn(lib_fn, max(3, steps // 2))
+        except Exception as e:   # context only
+            lib_name = f"unavailable: {type(e).__name__}"
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -319,36 +362,22 @@ def run_case(spec: str, steps: int = 20, warmup: int = 5, flush_mode: str = "aut
         torch.cuda.synchronize()
         graph_us = st.elapsed_time(en) / 500 * 1e3
     l0 = lib.launch_count()
-    if flush is None:
-        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        st.record()
-        for _ in range(steps):
-            fn()
-        en.record()
-        torch.cuda.synchronize()
-        ms = st.elapsed_time(en) / steps
-    else:   # small working set: write a buffer larger than L2 between timed launches
-        tot = 0.0
-        for _ in range(steps):
-            flush.zero_()
-            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            st.record()
-            fn()
-            en.record()
-            torch.cuda.synchronize()
-            tot += st.elapsed_time(en)
-        ms = tot / steps
+    ms = time_fn(fn, steps)
     launches = (lib.launch_count() - l0) // steps
+    assert lib.device_error() == 0, "a kernel reported a bounded-wait time-out"
     r = {"case": spec, "ms": ms, "value": work / ms / 1e9, "unit": unit, "launches_per_step": int(launches),
          "l2": "flushed between launches" if flush is not None else "working set larger than L2"}
     if graph_us is not None:
         r["us_per_launch_graph_replay"] = graph_us
+    if lib_name is not None:
+        r["library"] = {"what": lib_name, "ms": lib_ms, "value": (work / lib_ms / 1e9 if lib_ms else None), "unit": unit,
+                        "time_ratio_ours_over_library": (ms / lib_ms if lib_ms else None)}
     if kind in ("decode", "llama2"):
         r["roofline"] = {"bound": "hbm", "achieved": bytes_ / ms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": bytes_ / ms / 1e6 / peaks["hbm"]}
     elif kind == "int8":
         r["roofline"] = {"bound": "tensor", "achieved": work / ms / 1e9, "peak": 4500.0, "unit": "TOP/s", "frac": work / ms / 1e9 / 4500.0,
-                         "peak_source": "vendor dense int8 (no measured int8 figure on this pool)"}
+                         "peak_source": "vendor dense int8; the library figure of the 8192^3 case in the same sweep is the measured one"}
     else:
         r["roofline"] = {"bound": "tensor", "achieved": work / ms / 1e9, "peak": peaks["burst"], "unit": "TFLOP/s",
                          "frac": work / ms / 1e9 / peaks["burst"], "frac_of_vendor_dense_2250": work / ms / 1e9 / 2250.0}
@@ -434,8 +463,17 @@ def run_sharded_case(spec: str, steps: int, warmup: int, rank: int, world: int):
             "timing": "CUDA events, max over ranks, inputs resident"}
 
 
-SWEEP = ["cfg1", "int8:1024:4096:4096", "decode", "attention:16:32:2048:128:0", "attention:16:32:2048:128:1", "gemm:1024:1024:1024",
-         "gemm:2048:2048:2048", "gemm:4096:4096:4096", "gemm:8192:8192:8192", "gemm:16384:16384:16384"]
+def parallelism_of(world: int) -> str:
+    """How the workload is spread over `world` GPUs: a function of the launch alone, so that the reference arm
+    (which runs on the host) and this arm print the same `config`."""
+    if world == 1:
+        return "single GPU"
+    return (f"tp{world}: layers 1,3 column-parallel, layers 2,4 row-parallel, f32 partial sums exchanged between the GPUs' "
+            "own kernels over NVLink")
+
+
+SWEEP = ["cfg1", "int8:1024:4096:4096", "int8:8192:8192:8192", "decode", "attention:16:32:2048:128:0", "attention:16:32:2048:128:1",
+         "gemm:1024:1024:1024", "gemm:2048:2048:2048", "gemm:4096:4096:4096", "gemm:8192:8192:8192", "gemm:16384:16384:16384"]
 
 
 # --------------------------------------------------------------------------------------- GPU arm
@@ -446,7 +484,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--sweep", action="store_true", help="also time the other BASELINE configs (extra key 'sweep')")
+    ap.add_argument("--sweep", dest="sweep", action="store_true", default=True,
+                    help="also time the other BASELINE configs, each beside the vendor library on the same tensors (extra key 'sweep'; default)")
+    ap.add_argument("--no-sweep", dest="sweep", action="store_false", help="headline workload only (profiling runs)")
     ap.add_argument("--case", default=None, help="time ONE kernel-level case instead (see run_case) and print its line; "
                                                   "used for ncu captures of a single kernel")
     ap.add_argument("--flush", default="auto", choices=["auto", "on", "off"],
@@ -461,12 +501,15 @@ def main():
     config = {"workload": WORKLOAD, "batch": BATCH, "hidden": list(HIDDEN), "fill": "src N(0,1), weights N(0,0.02), bias 0 (benchgc fill flags)",
               "l2": "inputs larger than L2 (weights 512 MiB are re-read every step)"}
 
+    config["parallelism"] = parallelism_of(world)
     if a.impl == "reference":
         if rank != 0:
             return
-        r = cpu_reference_run(max(1, min(a.steps, 3)), min(a.warmup, 1))
+        # every step is a bounded sample (16 of the 512 batch rows through all four layers), so that the requested
+        # step and warm-up counts are honoured and the whole run still ends within a few minutes on the host cores
+        r = cpu_reference_run(max(1, a.steps), a.warmup, rows=16)
         line = {"impl": "reference", "metric": "TFLOPS", "value": r["value"], "unit": "TFLOPS", "n_gpus": a.gpus,
-                "steps": max(1, min(a.steps, 3)), "warmup": min(a.warmup, 1), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+                "steps": max(1, a.steps), "warmup": a.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
                 "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": r["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -613,7 +656,7 @@ def main():
                           "peer_reduce_scatter": "GEMM-epilogue peer stores over NVLink to the row owner (reduce-scatter), owner reduces "
                                                  "and stores the bf16 rows to every rank (all-gather)",
                           "all_reduce": "NCCL all-reduce"}[exchange.name] + ("; one CUDA-graph replay per step" if graph is not None else "") + why)
-    config["parallelism"] = parallelism
+    exchange_note = parallelism
 
     def barrier():
         if world > 1:
@@ -673,6 +716,7 @@ def main():
                          "last layer run as two row blocks so that the H2D / D2H copies overlap the other block's math") if world == 1 else
                         "per step: H2D of the activations on every rank, the tensor-parallel step, D2H of the result on rank 0"},
         "gpu_launches": int(gemm_launches),
+        "exchange": exchange_note,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s", "frac": achieved / peaks[peak_kind],
                      "traffic": traffic, "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind}",
@@ -687,7 +731,7 @@ def main():
         except Exception as e:  # context only
             line["cpu_onednn_class"] = {"error": repr(e)[:100]}
     if a.sweep and world == 1:
-        line["sweep"] = [run_case(c, 10 if "16384" in c else 20, 3) for c in SWEEP]
+        line["sweep"] = [run_case(c, 10 if "16384" in c else 20, 3, library=True) for c in SWEEP]
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

@@ -269,6 +269,8 @@ struct dnnl_graph_compiler_executable {
   mutable DeviceBuffer arena;
   mutable std::vector<DeviceBuffer> in_stage, out_stage;
   mutable std::vector<char> comp_ready; // per QMATMUL scratch: column sums computed for a cached constant weight
+  mutable DeviceBuffer splitk;          // split-K partial planes of this executable's matmul steps (they run one after
+                                        // another on one stream, so one block sized for the largest request serves all)
 
   explicit dnnl_graph_compiler_executable(const std::string &json) : plan(build_plan(read_partition(json))) {}
   ~dnnl_graph_compiler_executable() {
@@ -300,6 +302,21 @@ struct dnnl_graph_compiler_executable {
     in_stage.resize(plan.part.input_ids.size());
     out_stage.resize(plan.part.output_ids.size());
     comp_ready.assign(plan.scratch.size(), 0);
+    {
+      // split-K scratch of every matmul step, as the selector sees the shapes on this device (whole step and,
+      // where the step may run as row blocks, one block); a configuration recorded later that needs more
+      // falls back to the per-device workspace inside matmul_tc
+      size_t need = 0;
+      for (const Step &st : plan.steps) {
+        if (st.kind != StepKind::MATMUL && st.kind != StepKind::QMATMUL) continue;
+        const bool q = st.kind == StepKind::QMATMUL;
+        if (!q && plan.part.tensors.at(st.in[0]).dtype != DType::BF16) continue;
+        need = std::max(need, matmul_scratch_bytes(st.M, st.N, st.K, q ? 1 : 2, q ? 4 : 2, d.sm_count));
+        if (!q && rows_chunkable(st))
+          need = std::max(need, matmul_scratch_bytes(st.M / kRowChunks, st.N, st.K, 2, 2, d.sm_count));
+      }
+      if (need) splitk.reserve(need);
+    }
     ready = true;
   }
 
@@ -347,6 +364,7 @@ struct dnnl_graph_compiler_executable {
     m.B = b; m.M = rows; m.N = st.N; m.K = st.K; m.trans_a = 0; m.trans_b = st.trans_b;
     m.out_kind = OUT_BF16; m.out = static_cast<uint8_t *>(out) + size_t(r0) * size_t(st.N) * 2;
     m.bias_kind = bias ? BIAS_BF16 : BIAS_NONE; m.bias = bias; m.relu = st.relu;
+    m.scratch = splitk.ptr; m.scratch_bytes = splitk.bytes;
     matmul_tc(m, s);
   }
 
@@ -392,7 +410,12 @@ struct dnnl_graph_compiler_executable {
           b.reserve(bytes);
           GCB_CUDA(cudaMemcpyAsync(b.ptr, t->data, bytes, cudaMemcpyHostToDevice, s));
           b.cached_host = lt.constant ? t->data : nullptr;
-          for (size_t k = 0; k < comp_ready.size(); ++k) comp_ready[k] = 0;
+          // column sums depend on the weights alone: only those computed from THIS argument are stale now
+          for (const Step &qs : plan.steps)
+            if (qs.kind == StepKind::QMATMUL && qs.scratch_slot >= 0) {
+              const TensorSlot &ws = plan.slots.at(qs.in[1]);
+              if (ws.where == TensorSlot::INPUT && size_t(ws.index) == i) comp_ready[size_t(qs.scratch_slot)] = 0;
+            }
         }
         in_ptr[i] = b.ptr;
       }
@@ -573,6 +596,7 @@ struct dnnl_graph_compiler_executable {
           m.A = a; m.B = b; m.M = st.M; m.N = st.N; m.K = st.K; m.trans_a = st.trans_a; m.trans_b = st.trans_b;
           m.out_kind = OUT_BF16; m.out = addr(st.out[0]);
           m.bias_kind = bias ? BIAS_BF16 : BIAS_NONE; m.bias = bias; m.relu = st.relu;
+          m.scratch = splitk.ptr; m.scratch_bytes = splitk.bytes;
           matmul_tc(m, s);
         } else {
           matmul_simt(a, b, bias, addr(st.out[0]), st.M, st.N, st.K, st.trans_a, st.trans_b, 1, st.relu, s);
@@ -605,6 +629,7 @@ struct dnnl_graph_compiler_executable {
       m.relu = st.relu;
       if (!(tma_compatible(m.A, st.K, 1) && tma_compatible(m.B, st.N, 1)))
         throw std::logic_error("QuantizedMatMul needs K and N to be multiples of 16");
+      m.scratch = splitk.ptr; m.scratch_bytes = splitk.bytes;
       matmul_tc(m, s);
       break;
     }

@@ -19,7 +19,7 @@
 namespace gcb {
 
 constexpr int kThreads2 = 224;
-constexpr int kStaging2 = 4096;
+constexpr int kStaging2 = 8192;   // per epilogue warp: two slabs of 32 rows x 128 B
 constexpr int kMaxStages2 = 8;
 
 struct PairBarriers {
@@ -85,6 +85,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   cluster_sync_all();   // both CTAs' barriers are initialised before any cross-CTA signal
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&bars->tmem_base);
+  // the set-up above touched only shared and tensor memory and may overlap the tail of the kernel ahead
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -181,6 +184,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;
     uint8_t *stg = staging + (warp - 2) * kStaging2;
     uint32_t tcount = 0;
+    uint32_t slab = 0;   // TMA-store form: staging slab to fill next
     for (int u = pair; u < units; u += pairs, ++tcount) {
       const int tile = u / p.splits, split = u - tile * p.splits;
       int tm, tn;
@@ -192,11 +196,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * uint32_t(p.BN) + (uint32_t(q * 32) << 16);
-      gemm_epilogue_tile<KIND, false>(p, t_addr, tm * 256 + int(rank) * 128, tn * p.BN, split, q, lane, stg);
+      if (p.tma_store) gemm_epilogue_tile_tma<KIND>(p, t_addr, tm * 256 + int(rank) * 128, tn * p.BN, split, q, lane, stg, slab);
+      else gemm_epilogue_tile<KIND, false>(p, t_addr, tm * 256 + int(rank) * 128, tn * p.BN, split, q, lane, stg);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
     }
+    // the staging slabs must outlive the copy engine's reads, the stores must land before the grid ends
+    if (p.tma_store && lane == 0) tma_store_wait<0>();
   }
 
   // ---------------------------------------------------------------------- tear-down
@@ -222,8 +229,17 @@ cudaError_t launch_gemm_pair_kernel(const CUtensorMap &tmA, const CUtensorMap &t
     if (e != cudaSuccess) return e;
     configured[dev & 63] = true;
   }
-  kfn<<<grid & ~1, kThreads2, smem, stream>>>(tmA, tmB, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(grid & ~1));
+  cfg.blockDim = dim3(kThreads2);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, p);
 }
 
 template cudaError_t launch_gemm_pair_kernel<0>(const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, size_t,

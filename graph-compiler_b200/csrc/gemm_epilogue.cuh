@@ -73,7 +73,9 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
       __syncwarp();
       // ------------------------------------------------------------ store phase
       const int gcol = col0 + chunk * cpc;
-      const int nvalid = min(cpc, p.out_cols - gcol);   // <= 0: this chunk is beyond the last column
+      // <= 0: this chunk is beyond the last column of the output or of the tile (a tile whose width is not a
+      // whole number of slabs ends inside its last slab; the columns behind it belong to the next tile)
+      const int nvalid = min(cpc, min(p.out_cols, nn0 + p.BN) - gcol);
       uint32_t bias_b[8];
       float bias_f[4], scale_f[4];
       int32_t comp_i[4];
@@ -166,6 +168,14 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
       }
       __syncwarp();
     }
+    if (p.n_peers > 0 && p.peer_rows > 0 && p.signal_peer[0] != nullptr) {
+      // this warp's 32 rows of the tile are on their way to their owner: make them visible system-wide, then count
+      // the warp in at the owner (the owner's reduction waits for every warp of every tile of every rank)
+      __threadfence_system();
+      __syncwarp();
+      const int grow = row0 + q * 32;
+      if (lane == 0 && grow < p.out_rows) red_release_sys_add_u32(p.signal_peer[grow / p.peer_rows], 1u);
+    }
   } else {
   // ---- swapped orientation: MMA row = output column (this thread),
   //      MMA column = output row.  A warp stores 32 consecutive output
@@ -223,6 +233,84 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
 }
 }
 
+// The columns of a tile behind its last whole slab (tiles whose width is a multiple of 16 but not of the
+// slab width), 16 at a time: each thread owns one accumulator row, applies the same post-ops as the slab
+// form and stores its 16 columns itself (two or four 16-byte stores to consecutive addresses).
+// c0: first such column inside the tile; col0 = nn0 + c0; grow: this thread's output row.
+template <int KIND>
+__device__ __forceinline__ void gemm_epilogue_tail(const GemmParams &p, uint32_t t_addr, int c0, int col0, int grow, int split,
+                                                   int lane) {
+  const bool two_byte = (p.out_kind == OUT_BF16);
+  const size_t esz = two_byte ? 2 : 4;
+  const size_t plane = (p.splits > 1) ? size_t(split) * size_t(p.split_stride) : 0;
+  uint8_t *rowp = reinterpret_cast<uint8_t *>(p.out) + (plane + size_t(grow) * size_t(p.ld_out)) * esz;
+  const bool row_in = grow < p.out_rows;
+  for (int g0 = c0; g0 < p.BN; g0 += 16) {
+    const int gc = col0 + (g0 - c0);            // first output column of this group
+    if (gc >= p.out_cols) break;
+    uint32_t t[16];
+    tmem_ld_x16(t_addr + g0, t);
+    // post-op operands of column gc + lane (lanes 0..15), handed round by shuffles
+    uint32_t b16 = 0;
+    float q_scale = 1.f, q_bias = 0.f;
+    int32_t q_comp = 0;
+    {
+      const int c = gc + lane;
+      if (lane < 16 && c < p.out_cols) {
+        if (two_byte && p.bias_kind == BIAS_BF16) b16 = reinterpret_cast<const uint16_t *>(p.bias)[c];
+        if (p.out_kind == OUT_DEQUANT_F32) {
+          q_scale = p.scale[c];
+          if (p.bias_kind == BIAS_F32) q_bias = reinterpret_cast<const float *>(p.bias)[c];
+          if (p.comp) q_comp = p.comp[c];
+        }
+      }
+    }
+    tmem_wait_ld();
+    uint32_t w[16];
+    if (two_byte) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        uint32_t y = pack_bf16x2_rn(__uint_as_float(t[2 * e]), __uint_as_float(t[2 * e + 1]));   // first rounding
+        if (p.bias_kind == BIAS_BF16) {
+          const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, b16, 2 * e), b1 = __shfl_sync(0xFFFFFFFFu, b16, 2 * e + 1);
+          const float f0 = __fadd_rn(__uint_as_float(y << 16), __uint_as_float(b0 << 16));
+          const float f1 = __fadd_rn(__uint_as_float(y & 0xFFFF0000u), __uint_as_float(b1 << 16));
+          y = pack_bf16x2_rn(f0, f1);                                                               // second rounding
+        }
+        if (p.relu) y = bf16x2_relu(y);
+        w[e] = bf16x2_fix_nan(y);
+      }
+    } else if (p.out_kind == OUT_DEQUANT_F32) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float sc = __shfl_sync(0xFFFFFFFFu, q_scale, e), bi = __shfl_sync(0xFFFFFFFFu, q_bias, e);
+        const int32_t cp = __shfl_sync(0xFFFFFFFFu, q_comp, e);
+        float f = __fmul_rn(float(int32_t(t[e]) - cp), sc);
+        if (p.bias_kind == BIAS_F32) f = __fadd_rn(f, bi);
+        if (p.relu) f = (f != f) ? f : (f > 0.f ? f : 0.f);
+        w[e] = __float_as_uint(f);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) w[e] = t[e];
+    }
+    if (!row_in) continue;
+    uint8_t *g = rowp + size_t(gc) * esz;
+    if (gc + 16 <= p.out_cols) {
+      const int nvec = two_byte ? 2 : 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (i < nvec) reinterpret_cast<uint4 *>(g)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    } else {
+      const int nv = p.out_cols - gc;
+      for (int e = 0; e < nv; ++e) {
+        if (two_byte) reinterpret_cast<uint16_t *>(g)[e] = uint16_t(w[e >> 1] >> ((e & 1) * 16));
+        else          reinterpret_cast<uint32_t *>(g)[e] = w[e];
+      }
+    }
+  }
+}
+
 // TMA-store form of the row-major epilogue (bf16 with optional bias / ReLU, int8 dequantisation to f32, or
 // raw f32 / s32 planes).
 // Each thread owns one accumulator row: TMEM -> registers -> rounding and post-ops on packed pairs ->
@@ -240,6 +328,12 @@ __device__ __forceinline__ void gemm_epilogue_tile_tma(const GemmParams &p, uint
   for (int c0 = 0; c0 < p.BN; c0 += slab_cols) {
     const int col0 = nn0 + c0;
     if (col0 >= p.out_cols) break;
+    if (p.BN - c0 < slab_cols) {
+      // the tile is not a whole number of slabs wide (BN a multiple of 16 only): the last 16, 32 or 48 columns
+      // go from registers straight to global memory, 16 columns (32 or 64 contiguous bytes per row) at a time
+      gemm_epilogue_tail<KIND>(p, t_addr, c0, col0, grow0 + lane, split, lane);
+      break;
+    }
     uint32_t v[64];
     {
       uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);

@@ -116,6 +116,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool mn = g.mn_major != 0, one = g.one_load != 0, k3d = g.k3d != 0;
       const int bk = p.bk_elems, kpb = max(p.kpb, 1);
       int err = 0;
+      if (p.wait_counter != nullptr) {
+        // the activations are stored into this GPU's memory by other GPUs' kernels: wait for this step's rows
+        const uint32_t target = (*reinterpret_cast<const volatile uint32_t *>(p.epoch) + 1u) * p.wait_per_step;
+        if (!wait_counter_reached(p.wait_counter, target)) err = ERR_WAIT_PEER;
+        fence_proxy_async_global();
+      }
       for (int u = blockIdx.x; u < units && !err; u += gridDim.x) {
         const int tile = u / p.splits, split = u - tile * p.splits;
         int tm_, tn_;

@@ -15,6 +15,8 @@ enum ErrCode : int {
   ERR_WAIT_TMEM_EMPTY = 3, // MMA: an accumulator was never drained
   ERR_WAIT_TMEM_FULL = 4,  // epilogue: an accumulator was never committed
   ERR_WAIT_DRAIN = 5,      // tear-down: an issued copy did not land
+  ERR_WAIT_PEER = 6,       // a cross-GPU counter (rows landed / partial sums landed) never reached its target
+  ERR_SELFTEST = 7,        // the wait self-test: a wait nobody satisfies ran out, as intended
 };
 
 // Geometry of one operand's pipeline stage in shared memory and of the
@@ -69,6 +71,15 @@ struct GemmParams {
                         // peer d only, whose buffer is [planes][peer_rows][ld_out] (reduce-scatter by rows)
   int peer_multicast;   // 1: peer_out[0] is a multicast address covering every rank's buffer; one multimem store per chunk
   void *peer_out[8];
+  // Hand-off between GPUs without a host round trip (tensor-parallel layers; see sm100_ptx.cuh).
+  //  signal_peer[d] != null (row scatter only): after an epilogue warp has stored its 32 rows of a tile into owner d's
+  //    buffer it fences at system scope and adds 1 to this counter in d's memory;
+  //  wait_counter != null: both operand producers wait, before their first load, until this LOCAL counter has
+  //    reached (*epoch + 1) * wait_per_step - the rows of the activations that other GPUs store into this GPU's memory.
+  uint32_t *signal_peer[8];
+  const uint32_t *wait_counter;
+  const uint32_t *epoch;
+  uint32_t wait_per_step;
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
   // TMA-store epilogue (one-CTA kernel, row-major orientation): tmC covers the output as
   // [planes][rows][cols] with a box of {128 bytes of columns, 32 rows, 1}; each epilogue warp hands its

@@ -343,7 +343,7 @@ Plan build_plan(Partition part) {
       // ---- fuse a following Add(bias [N]) and ReLU: the post-ops the reference pulls into the tile loop
       size_t cur_out = Y.id, next = oi + 1;
       if (!st.has_bias && next < p.ops.size() && !consumed[next] && p.ops[next].kind == "Add" &&
-          p.ops[next].inputs.size() == 2 && single_use_temp(cur_out)) {
+          p.ops[next].inputs.size() == 2 && p.ops[next].outputs.size() == 1 && single_use_temp(cur_out)) {
         const GraphOp &add = p.ops[next];
         int mi = add.inputs[0].id == cur_out ? 0 : (add.inputs[1].id == cur_out ? 1 : -1);
         if (mi >= 0) {
@@ -360,8 +360,8 @@ Plan build_plan(Partition part) {
           }
         }
       }
-      if (next < p.ops.size() && !consumed[next] && p.ops[next].kind == "ReLU" && p.ops[next].inputs[0].id == cur_out &&
-          single_use_temp(cur_out)) {
+      if (next < p.ops.size() && !consumed[next] && p.ops[next].kind == "ReLU" && p.ops[next].inputs.size() == 1 &&
+          p.ops[next].outputs.size() == 1 && p.ops[next].inputs[0].id == cur_out && single_use_temp(cur_out)) {
         st.relu = true;
         cur_out = p.ops[next].outputs[0].id;
         consumed[next] = true;
@@ -470,11 +470,28 @@ Plan build_plan(Partition part) {
       st.scratch_slot = int(plan.scratch.size());
       plan.scratch.push_back(TensorSlot{TensorSlot::ARENA, 0, 0, size_t(st.N) * 4});
       scratch_reqs.emplace_back(lives.size(), int(si));
-      lives.push_back(BufferLife{size_t(st.N) * 4, int(si), int(si)});
+      // The column sums of a constant weight are computed by the first call and kept for the following ones,
+      // so their region must not be handed to any other temporary: it is live over every step (and, as the
+      // arena belongs to the executable, from one call to the next).
+      lives.push_back(BufferLife{size_t(st.N) * 4, 0, int(plan.steps.size()) - 1});
     }
   }
-  // an output may also be consumed by a later op; a partition argument that is
-  // also listed as an output is not produced here and is left alone
+  // an output may also be consumed by a later op.  Results are written densely: an output declared with
+  // other strides, or an output that is one of the partition's own arguments (nothing here produces it),
+  // is refused at compile time instead of returning memory nobody wrote.
+  for (size_t id : p.output_ids) {
+    const LogicalTensor &t = p.tensors.at(id);
+    if (std::find(p.input_ids.begin(), p.input_ids.end(), id) != p.input_ids.end())
+      unsupported("output " + std::to_string(id) + " is a partition input: pass-through outputs are not supported");
+    if (t.strided && t.stride.size() == t.shape.size()) {
+      int64_t expect = 1;
+      for (int d = int(t.shape.size()) - 1; d >= 0; --d) {
+        if (t.shape[size_t(d)] != 1 && t.stride[size_t(d)] != expect)
+          unsupported("output " + std::to_string(id) + " has non-dense strides: results are written row-major dense");
+        expect *= t.shape[size_t(d)];
+      }
+    }
+  }
   std::vector<size_t> offsets;
   plan.arena_bytes = plan_arena(lives, 1024, offsets);
   for (size_t i = 0; i < live_ids.size(); ++i) plan.slots[live_ids[i]].offset = offsets[live_index[live_ids[i]]];

@@ -22,6 +22,8 @@
 // that device current) and configures the kernel's shared-memory limit; make that first call
 // before any stream capture begins.
 #include <algorithm>
+#include <cstdint>
+#include <exception>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -97,7 +99,33 @@ __global__ void static_reduce_kernel(int splits, long long M, long long N, const
   }
 }
 
+// The same reduction four columns at a time with 16-byte loads (N is a multiple of 8 here, so rows and planes
+// keep float4 alignment): same additions in the same order, same two roundings, packed conversions.
+__global__ void __launch_bounds__(256)
+static_reduce_x4_kernel(int splits, long long total4, int n4, const uint2 *bias, uint2 *out, int relu) {
+  const float4 *planes = reinterpret_cast<const float4 *>(g_static_scratch);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    float4 s = planes[i];
+    for (int k = 1; k < splits; ++k) {
+      const float4 t = planes[(long long)k * total4 + i];
+      s.x = __fadd_rn(s.x, t.x); s.y = __fadd_rn(s.y, t.y); s.z = __fadd_rn(s.z, t.z); s.w = __fadd_rn(s.w, t.w);
+    }
+    uint32_t lo = pack_bf16x2_rn(s.x, s.y), hi = pack_bf16x2_rn(s.z, s.w);
+    if (bias) {
+      const uint2 b = bias[int(i % n4)];
+      lo = pack_bf16x2_rn(__fadd_rn(__uint_as_float(lo << 16), __uint_as_float(b.x << 16)),
+                          __fadd_rn(__uint_as_float(lo & 0xFFFF0000u), __uint_as_float(b.x & 0xFFFF0000u)));
+      hi = pack_bf16x2_rn(__fadd_rn(__uint_as_float(hi << 16), __uint_as_float(b.y << 16)),
+                          __fadd_rn(__uint_as_float(hi & 0xFFFF0000u), __uint_as_float(b.y & 0xFFFF0000u)));
+    }
+    if (relu) { lo = bf16x2_relu(lo); hi = bf16x2_relu(hi); }
+    out[i] = make_uint2(bf16x2_fix_nan(lo), bf16x2_fix_nan(hi));
+  }
+}
+
 } // namespace
+
+int guard_status(const std::exception_ptr &ep);   // capi_kernels.cu: exception -> gcb200_status, message kept
 } // namespace gcb
 
 using namespace gcb;
@@ -106,6 +134,7 @@ GCB_EXPORT int gcb200_matmul_bf16_splitk_static(const void *A, const void *B, co
                                                 int64_t N, int64_t K, int splits, int relu, void *stream_) {
   try {
     if (!A || !B || !Y || M <= 0 || N <= 0 || K <= 0) throw std::invalid_argument("bad arguments");
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) throw std::invalid_argument("M, N and K must fit 31 bits");
     if (!(tma_compatible(A, K, 2) && tma_compatible(B, N, 2)))
       throw std::invalid_argument("operands need 16-byte aligned bases and row pitches (K and N multiples of 8)");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -118,9 +147,11 @@ GCB_EXPORT int gcb200_matmul_bf16_splitk_static(const void *A, const void *B, co
     want = std::max(1, std::min(want, k_blocks));
     const int per = (k_blocks + want - 1) / want;
     cfg.splits = (k_blocks + per - 1) / per;     // every split owns at least one K block
-    const size_t need = size_t(cfg.splits) * size_t(M) * size_t(N) * 4;
-    if (need > kStaticScratchBytes)
-      throw std::invalid_argument("splits * M * N * 4 = " + std::to_string(need) + " bytes exceeds the static scratch of " +
+    // compare by division: the product itself can wrap for absurd sizes and then pass a plain comparison
+    const size_t plane_elems_max = kStaticScratchBytes / 4 / size_t(cfg.splits);
+    if (size_t(M) > plane_elems_max / size_t(N))
+      throw std::invalid_argument("splits * M * N * 4 = " + std::to_string(cfg.splits) + " * " + std::to_string(M) + " * " +
+                                  std::to_string(N) + " * 4 bytes exceeds the static scratch of " +
                                   std::to_string(kStaticScratchBytes) + " bytes");
 
     GemmParams p{};
@@ -164,21 +195,22 @@ GCB_EXPORT int gcb200_matmul_bf16_splitk_static(const void *A, const void *B, co
     if (e != cudaSuccess) throw CudaError(std::string("gemm launch: ") + cudaGetErrorString(e));
     count_launch();
     const long long total = M * N;
-    const int blocks = int(std::min<long long>((total + 255) / 256, (long long)st.sm_count * 8));
-    static_reduce_kernel<<<blocks, 256, 0, stream>>>(cfg.splits, M, N, static_cast<const uint16_t *>(bias),
-                                                     static_cast<uint16_t *>(Y), relu);
+    auto al8 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 7) == 0; };
+    if (N % 4 == 0 && al8(Y) && (!bias || al8(bias))) {
+      const long long total4 = total / 4;
+      const int blocks = int(std::min<long long>((total4 + 255) / 256, (long long)st.sm_count * 8));
+      static_reduce_x4_kernel<<<std::max(blocks, 1), 256, 0, stream>>>(cfg.splits, total4, int(N / 4), static_cast<const uint2 *>(bias),
+                                                                      static_cast<uint2 *>(Y), relu);
+    } else {
+      const int blocks = int(std::min<long long>((total + 255) / 256, (long long)st.sm_count * 8));
+      static_reduce_kernel<<<blocks, 256, 0, stream>>>(cfg.splits, M, N, static_cast<const uint16_t *>(bias),
+                                                       static_cast<uint16_t *>(Y), relu);
+    }
     GCB_CUDA(cudaGetLastError());
     count_launch();
     return GCB200_OK;
-  } catch (const CudaError &e) {
-    g_last_error = e.what();
-    return g_last_error.rfind("no CUDA device", 0) == 0 ? GCB200_NO_DEVICE : GCB200_CUDA_ERROR;
-  } catch (const std::invalid_argument &e) {
-    g_last_error = e.what();
-    return GCB200_INVALID_ARGUMENT;
-  } catch (const std::exception &e) {
-    g_last_error = e.what();
-    return GCB200_CUDA_ERROR;
+  } catch (...) {
+    return guard_status(std::current_exception());   // same status classes as every other entry point
   }
 }
 
@@ -191,11 +223,7 @@ GCB_EXPORT int gcb200_static_error(void *stream, int *code) {
     GCB_CUDA(cudaStreamSynchronize(s));
     if (*code != 0) GCB_CUDA(cudaMemsetAsync(st.error, 0, sizeof(int), s));
     return GCB200_OK;
-  } catch (const std::invalid_argument &e) {
-    g_last_error = e.what();
-    return GCB200_INVALID_ARGUMENT;
-  } catch (const std::exception &e) {
-    g_last_error = e.what();
-    return GCB200_CUDA_ERROR;
+  } catch (...) {
+    return guard_status(std::current_exception());
   }
 }

@@ -36,21 +36,25 @@ DeviceState &device_state() {
       throw CudaError("this library is built for sm_100a only; device is sm_" + std::to_string(prop.major) +
                       std::to_string(prop.minor));
     d.sm_count = prop.multiProcessorCount;
-    GCB_CUDA(cudaMalloc(&d.d_error, sizeof(int)));
-    GCB_CUDA(cudaMemset(d.d_error, 0, sizeof(int)));
+    GCB_CUDA(cudaMalloc(&d.d_error, 64));
+    GCB_CUDA(cudaMemset(d.d_error, 0, 64));
+    d.d_zero = d.d_error + 8;
     d.device = dev;
   }
   return d;
 }
 
 void *DeviceState::ensure_workspace(size_t bytes) {
+  std::lock_guard<std::mutex> g(g_dev_mutex);
   if (bytes <= workspace_bytes) return workspace;
-  GCB_CUDA(cudaDeviceSynchronize());
-  if (workspace) GCB_CUDA(cudaFree(workspace));
-  workspace = nullptr;
-  workspace_bytes = 0;
-  size_t want = std::max(bytes, size_t(64) << 20);
-  GCB_CUDA(cudaMalloc(&workspace, want));
+  // Grow by allocating a larger block and keeping the old one until the process exits: launches already
+  // queued (or captured in a graph) on another stream or by another thread keep a valid address, and
+  // nothing here synchronises the device or frees memory under a caller's feet.  Sizes at least double,
+  // so the retired blocks add up to less than the live one.
+  const size_t want = std::max({bytes, workspace_bytes * 2, size_t(64) << 20});
+  void *fresh = nullptr;
+  GCB_CUDA(cudaMalloc(&fresh, want));
+  workspace = fresh;   // the previous block is retired, not freed
   workspace_bytes = want;
   ++workspace_generation;
   return workspace;
@@ -243,6 +247,11 @@ MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byte
   return c;
 }
 
+size_t matmul_scratch_bytes(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count) {
+  const MatmulConfig c = select_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count);
+  return c.splits > 1 ? size_t(c.splits) * size_t(M) * size_t(N) * 4 : 0;
+}
+
 // ----------------------------------------------------------------------------- matmul planning
 OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes, int kpb) {
   OperandGeom g{};
@@ -276,11 +285,12 @@ OperandGeom operand_geom(bool mn_major, int tile_mn, int elem_bytes, int kpb) {
 CUtensorMap operand_tmap(OperandGeom &g, ElemType t, int elem_bytes, const void *ptr, int64_t mn_total,
                                 int64_t k_total, int tile_mn, int kpb) {
   const uint32_t bk = 128 / elem_bytes;
-  if (g.mn_major && elem_bytes == 2 && mn_total % int64_t(g.box_mn) == 0) {
+  if (g.mn_major && elem_bytes == 2 && mn_total % int64_t(g.box_mn) == 0 && tile_mn % int(g.box_mn) == 0) {
     // memory [k_total][mn_total] seen as [group][k][128 bytes]: one copy brings all 64-wide (128-byte)
     // groups of the tile, landing as consecutive [rows x 128 B] blocks — the layout the MMA reads.
     // Only when MN is a whole number of groups: a partial last group would make the copy read past
-    // the end of the last row.  16-bit operands only: the same 3-D form on 8-bit operands returned
+    // the end of the last row; and only when the tile is a whole number of groups wide, so that every
+    // tile starts on a group boundary (tiles of 16 x odd columns take one 2-D copy per group instead).  16-bit operands only: the same 3-D form on 8-bit operands returned
     // wrong data for the second group at small N on B200, so those keep one 2-D copy per group.
     g.one_load = 1;
     return make_tmap_3d(t, ptr, g.box_mn, uint64_t(k_total), uint64_t(mn_total) / g.box_mn,
@@ -386,17 +396,31 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
     p.peer_plane = a.peer_plane;
     p.peer_rows = a.peer_rows;
     for (int d = 0; d < a.n_peers; ++d) p.peer_out[d] = a.peer_out[d];
+    if (a.signal_peer) {
+      // one increment per epilogue warp (32 rows) and tile: a warp's rows must all belong to one owner
+      if (a.peer_rows <= 0 || a.peer_rows % 32 || cfg.swapped || a.M % 128)
+        throw std::invalid_argument("counted row scatter needs rows per peer that are a multiple of 32, M a multiple of 128 and the row-major kernel");
+      for (int d = 0; d < a.n_peers; ++d) {
+        if (!a.signal_peer[d]) throw std::invalid_argument("null peer counter");
+        p.signal_peer[d] = a.signal_peer[d];
+      }
+      if (a.arrivals_per_peer) *a.arrivals_per_peer = p.tiles_n * (a.peer_rows / 32);
+    }
+  }
+  if (a.wait_counter) {
+    if (!a.epoch) throw std::invalid_argument("a counter wait needs the step counter");
+    p.wait_counter = a.wait_counter;
+    p.epoch = a.epoch;
+    p.wait_per_step = a.wait_per_step;
   }
   const bool split = cfg.splits > 1;
   void *planes = nullptr;
   if (split) {
     const size_t need = size_t(cfg.splits) * size_t(a.M) * size_t(a.N) * 4;
-    if (a.scratch) {
-      if (a.scratch_bytes < need) throw std::invalid_argument("split-K scratch too small");
-      planes = a.scratch;
-    } else {
-      planes = dev.ensure_workspace(need);
-    }
+    // the caller's scratch (an executable's own, sized when it was prepared) when it is large enough; the
+    // per-device workspace otherwise (direct launchers, or a configuration recorded after the executable was prepared)
+    if (a.scratch && a.scratch_bytes >= need) planes = a.scratch;
+    else planes = dev.ensure_workspace(need);
     p.out_kind = a.int8 ? OUT_S32 : OUT_F32;
     p.out = planes;
     p.ld_out = a.N;
@@ -418,7 +442,7 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   }
   // TMA-store epilogue: bf16 outputs (bias / ReLU applied in registers) and raw f32 / s32 planes, when the
   // copy engine can address the output (16-byte aligned base and row pitch)
-  if (!pair && !cfg.swapped && a.n_peers == 0 && p.acc_dump == nullptr) {
+  if (!cfg.swapped && a.n_peers == 0 && p.acc_dump == nullptr) {
     const int esz = p.out_kind == OUT_BF16 ? 2 : 4;
     const bool plain = p.out_kind == OUT_BF16          ? (p.bias_kind == BIAS_NONE || p.bias_kind == BIAS_BF16)
                        : p.out_kind == OUT_DEQUANT_F32 ? (p.bias_kind == BIAS_NONE || p.bias_kind == BIAS_F32)

@@ -30,10 +30,14 @@ struct DeviceState {
   int device = -1;
   int sm_count = 0;
   int *d_error = nullptr;          // device word written by kernels on a bounded-wait time-out
-  void *workspace = nullptr;       // split-K partial planes, column sums
+  int *d_zero = nullptr;           // device word that stays zero (the wait self-test waits on it)
+  // Split-K partial planes of the direct launchers (executables bring their own scratch).  ONE block per
+  // device, shared by every stream and thread: launches that may split K and overlap on the GPU must be
+  // serialised by the caller.  Growing it never frees the old block (see ensure_workspace).
+  void *workspace = nullptr;
   size_t workspace_bytes = 0;
-  unsigned long long workspace_generation = 0;   // bumped whenever the workspace moves (captured graphs hold its address)
-  void *ensure_workspace(size_t bytes); // grows (synchronising) when needed
+  unsigned long long workspace_generation = 0;   // bumped whenever a larger block replaces the workspace
+  void *ensure_workspace(size_t bytes); // thread-safe; grows by allocating a larger block
 };
 DeviceState &device_state();       // throws CudaError when no usable device / driver
 
@@ -63,6 +67,8 @@ struct MatmulConfig {
 MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
 // The fitted time model alone (select_matmul_config consults the measured configurations of tune_cache.h first).
 MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
+// Bytes of f32 / s32 split-K partial planes the selected configuration of this shape needs (0: no split).
+size_t matmul_scratch_bytes(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
 // Whether the TMA path can take this operand layout (16-byte aligned base and row pitch).
 bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes);
 
@@ -99,6 +105,12 @@ struct MatmulArgs {
   const MatmulConfig *force = nullptr; // optional override
   void *scratch = nullptr;      // optional caller-provided split-K scratch (else the device workspace)
   size_t scratch_bytes = 0;
+  // cross-GPU hand-off (see GemmParams): counters to add to after the row scatter, counter to wait for before loading
+  uint32_t *const *signal_peer = nullptr;   // [n_peers], with peer_rows > 0 (rows per peer a multiple of 32)
+  const uint32_t *wait_counter = nullptr;
+  const uint32_t *epoch = nullptr;          // required with wait_counter
+  uint32_t wait_per_step = 0;
+  int *arrivals_per_peer = nullptr;         // out: counter increments each peer receives from this launch
 };
 void matmul_tc(const MatmulArgs &a, cudaStream_t stream);
 

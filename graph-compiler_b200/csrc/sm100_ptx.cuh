@@ -342,6 +342,36 @@ __device__ __forceinline__ void multimem_st_16(void *mc_addr, uint4 v) {
                : "memory");
 }
 
+// ----------------------------------------------------------------------------- cross-GPU hand-off
+// Monotonic counters in peer-mapped device memory order work between kernels on different GPUs without a
+// host round trip: a producer stores its data (plain stores, possibly to a peer), fences at system scope and
+// adds to the consumer's counter; the consumer polls its LOCAL counter with an acquire load.  Counters are
+// never reset: step n waits for (n + 1) x (arrivals per step), compared with wrap-around arithmetic.
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(uint32_t *p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait until *p has reached `target`.  Returns false on time-out (the caller records an error code and
+// leaves through its normal tear-down).  The sleep keeps the poll off the issue slots of the working warps.
+__device__ __forceinline__ bool wait_counter_reached(const uint32_t *p, uint32_t target, long long limit_cycles = WAIT_LIMIT_CYCLES) {
+  if (int32_t(ld_acquire_sys_u32(p) - target) >= 0) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (int32_t(ld_acquire_sys_u32(p) - target) >= 0) return true;
+      __nanosleep(40);
+    }
+    if (clock64() - t0 > limit_cycles) return false;
+  }
+}
+// Orders the generic-proxy acquire above before later async-proxy reads (TMA loads) of the same global memory.
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
 // cvt.rn.bf16x2 returns 0x7FFF for a NaN input; the reference conversion returns 0x7FC0
 // (BrgemmInterface.h:83-92).  Patch the (rare) NaN halves of a packed pair.
 __device__ __forceinline__ uint32_t bf16x2_fix_nan(uint32_t w) {

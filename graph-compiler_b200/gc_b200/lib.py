@@ -32,6 +32,14 @@ class MatmulConfig(C.Structure):
                 f"group_m={self.group_m}, grid={self.grid}, pair={self.pair}, kpb={self.kpb})")
 
 
+class TpMlpDesc(C.Structure):
+    """Mirror of ``gcb200_tp_mlp_desc``."""
+
+    _fields_ = [("world", _int), ("rank", _int), ("batch", _i64), ("layers", _int), ("hidden", C.POINTER(_i64)),
+                ("weights", C.POINTER(_vp)), ("biases", C.POINTER(_vp)), ("relu", _int),
+                ("recv", C.POINTER(_vp) * 2), ("act", C.POINTER(_vp) * 2), ("signals", C.POINTER(_vp)), ("x_in", C.POINTER(_vp))]
+
+
 _lib = None
 
 
@@ -74,6 +82,12 @@ def load() -> C.CDLL:
         "gcb200_tune_cache_save": [C.c_char_p, C.POINTER(_int)],
         "gcb200_tune_cache_erase": [_i64, _i64, _i64, _int, _int],
         "gcb200_tune_cache_clear": [],
+        "gcb200_tp_mlp_create": [C.POINTER(TpMlpDesc), C.POINTER(_vp)],
+        "gcb200_tp_mlp_destroy": [_vp],
+        "gcb200_tp_mlp_describe": [_vp, _int, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)],
+        "gcb200_tp_mlp_step": [_vp, _vp, _vp, C.POINTER(_vp)],
+        "gcb200_tp_mlp_execute": [_vp, _vp, _vp],
+        "gcb200_wait_selftest": [C.c_longlong, _vp],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -320,3 +334,62 @@ def attention_bf16(Q, K, V, scale: float, causal: bool = False, out=None):
         out = torch.empty_like(Q)
     check(load().gcb200_attention_bf16(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), bh, S, D, float(scale), int(causal), _stream()))
     return out
+
+
+class TpMlpPlan:
+    """Handle of a ``gcb200_tp_mlp`` plan: ``tables`` are lists of integer device addresses indexed by rank
+    (``recv0, recv1, act0, act1, signals`` and optionally ``x_in``), ``weights`` / ``biases`` lists of this rank's
+    shard addresses (0 / None = no bias).  Creating and describing a plan needs no device."""
+
+    def __init__(self, world, rank, batch, hidden, weights, biases, relu, recv, act, signals, x_in=None):
+        layers = len(hidden) - 1
+
+        def table(vals):
+            return (_vp * len(vals))(*[_vp(int(v)) if v else _vp(None) for v in vals])
+
+        self._keep = [(_i64 * len(hidden))(*hidden), table(weights), table(biases), table(recv[0]), table(recv[1]),
+                      table(act[0]), table(act[1]), table(signals), table(x_in) if x_in else None]
+        k = self._keep
+        d = TpMlpDesc()
+        d.world, d.rank, d.batch, d.layers, d.relu = world, rank, batch, layers, int(relu)
+        d.hidden = k[0]
+        d.weights = C.cast(k[1], C.POINTER(_vp))
+        d.biases = C.cast(k[2], C.POINTER(_vp))
+        d.recv[0], d.recv[1] = C.cast(k[3], C.POINTER(_vp)), C.cast(k[4], C.POINTER(_vp))
+        d.act[0], d.act[1] = C.cast(k[5], C.POINTER(_vp)), C.cast(k[6], C.POINTER(_vp))
+        d.signals = C.cast(k[7], C.POINTER(_vp))
+        d.x_in = C.cast(k[8], C.POINTER(_vp)) if x_in else C.POINTER(_vp)()
+        self._h = _vp(None)
+        check(load().gcb200_tp_mlp_create(C.byref(d), C.byref(self._h)))
+
+    def describe(self, sm_count: int = 148) -> str:
+        need = C.c_size_t(0)
+        check(load().gcb200_tp_mlp_describe(self._h, sm_count, None, 0, C.byref(need)))
+        buf = C.create_string_buffer(need.value)
+        check(load().gcb200_tp_mlp_describe(self._h, sm_count, buf, need.value, None))
+        return buf.value.decode()
+
+    def step(self, x_ptr: int, stream=None) -> int:
+        """Enqueues one step; returns the device address of this rank's copy of the result."""
+        res = _vp(None)
+        check(load().gcb200_tp_mlp_step(self._h, _vp(x_ptr), _stream() if stream is None else _vp(stream), C.byref(res)))
+        return int(res.value)
+
+    def execute(self, x_host_ptr: int, y_host_ptr: int = 0):
+        check(load().gcb200_tp_mlp_execute(self._h, _vp(x_host_ptr), _vp(y_host_ptr) if y_host_ptr else _vp(None)))
+
+    def destroy(self):
+        if self._h:
+            load().gcb200_tp_mlp_destroy(self._h)
+            self._h = _vp(None)
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def wait_selftest(limit_cycles: int = 1_000_000):
+    """Launches the failure-path self-test kernel (a bounded wait nothing satisfies) on the current stream."""
+    check(load().gcb200_wait_selftest(limit_cycles, _stream()))

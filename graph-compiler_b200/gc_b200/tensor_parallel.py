@@ -182,6 +182,78 @@ class PeerReduceScatterExchange:
         return self.outs[i]
 
 
+class FusedTensorParallelMLP:
+    """The tensor-parallel MLP step behind the C ABI (``gcb200_tp_mlp_*``, csrc/tp.cu): this class only allocates
+    the memory every rank can address (torch symmetric memory: plumbing) and hands the address tables to the
+    library, whose own kernels do the GEMMs, the exchange and every hand-off between GPUs (device counters, no
+    barrier kernels of another library, no host round trip between layers).
+
+    ``weight_shards`` / ``bias_shards`` as returned by ``shard_weights``; ``hidden`` the full layer widths."""
+
+    name = "fused_counters"
+
+    def __init__(self, weight_shards, bias_shards, batch: int, hidden, device, relu: bool = True, group=None, with_input: bool = True):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import lib
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.batch, self.hidden = batch, list(hidden)
+        self.w, self.b = list(weight_shards), list(bias_shards)
+        nmax = max(self.hidden[2::2])
+        self._bufs = []
+
+        def shared(shape, dtype):
+            t = symm.empty(shape, dtype=dtype, device=device)
+            h = symm.rendezvous(t, self.group)
+            self._bufs.append((t, h))
+            return t, [int(p) for p in h.buffer_ptrs]
+
+        self.recv, self.act, recv_p, act_p = [], [], [], []
+        for _ in range(2):
+            t, p = shared((self.world, batch // self.world, nmax), torch.float32)
+            self.recv.append(t); recv_p.append(p)
+            t, p = shared((batch, nmax), torch.bfloat16)
+            self.act.append(t); act_p.append(p)
+        self.signals, sig_p = shared((16,), torch.int32)
+        self.signals.zero_()
+        x_p = None
+        if with_input:
+            self.x_in, x_p = shared((batch, self.hidden[0]), torch.bfloat16)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)          # every rank's counters are zero before anyone adds to them
+        self.plan = lib.TpMlpPlan(self.world, self.rank, batch, self.hidden, [w.data_ptr() for w in self.w],
+                                  [0 if b is None else b.data_ptr() for b in self.b], relu, recv_p, act_p, sig_p, x_p)
+        self.launches_per_step = 3 * (len(self.w) // 2) + 1
+        self.collectives_per_step = 0
+        self._slot = (len(self.w) // 2 - 1) & 1
+        self._n_out = self.hidden[-1]
+
+    def _result(self):
+        t = self.act[self._slot]
+        return t if t.shape[1] == self._n_out else t.view(-1)[: self.batch * self._n_out].view(self.batch, self._n_out)
+
+    def step(self, x):
+        """x: bf16 [batch, hidden[0]] on this rank's device (the same values on every rank)."""
+        self.plan.step(x.data_ptr())
+        return self._result()
+
+    def execute(self, x_host, y_host=None):
+        """Synchronous host-buffer form (pinned tensors): every rank passes the same full input."""
+        self.plan.execute(x_host.data_ptr(), 0 if y_host is None else y_host.data_ptr())
+        return self._result()
+
+    def close(self):
+        import torch
+
+        torch.cuda.synchronize()
+        self.plan.destroy()
+        self._bufs.clear()
+
+
 class TensorParallelMLP:
     """An even number of bias+ReLU layers, sharded as described in the module docstring."""
 

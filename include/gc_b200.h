@@ -224,6 +224,69 @@ int gcb200_schedule_memory(const uint64_t *trace_buffer, const uint64_t *trace_s
                            uint64_t *total, uint64_t *sel_buffer, uint64_t *sel_reused, int *n_sel);
 
 /* ---------------------------------------------------------------------------
+ * Tensor-parallel MLP across the GPUs of one node: one process per GPU, each calling these with the same shapes.
+ * The across-device form of the reference's N and K thread splits (NThreads / KThreads,
+ * lib/gc/Transforms/DeepTileContractionOp.cpp:562-601; f32 partial sums reduced, then cast: :446-471, :988-996),
+ * behind the same call shape as dnnl_graph_compiler_execute (src/dnnl/dnnl_graph_compiler.cpp:214-226): build once,
+ * then one call per step.
+ *
+ * Layers 0, 2, ... are column-parallel (this rank's weight shard is [hidden[i], hidden[i+1] / world], its bias shard
+ * [hidden[i+1] / world]); layers 1, 3, ... are row-parallel (shard [hidden[i] / world, hidden[i+1]], whole bias).
+ * The f32 partial sums of a row-parallel layer leave the GEMM epilogue row block by row block for the rank that
+ * owns the rows; the owner reduces in rank order, applies bias / ReLU, casts once and stores the bf16 rows into every
+ * rank's activation buffer.  Hand-offs between GPUs are counters in device memory that this library's own kernels add to and
+ * wait on (bounded; a wait that runs out sets the device error word): no other library's kernel and no host round
+ * trip sits between the layers.  Every rank ends a step with the same bits.
+ *
+ * The caller provides the memory every rank can address (e.g. torch symmetric memory), as tables indexed by rank,
+ * this rank's own entry included:
+ *   recv[s][r]   f32  [world][batch / world][max row-parallel width]   partial sums, s = 0, 1 (consecutive exchanges alternate)
+ *   act[s][r]    bf16 [batch][max row-parallel width]                  reduced activations / the result
+ *   signals[r]   uint32[16], zeroed once before the first step (all ranks, then a barrier)
+ *   x_in[r]      bf16 [batch][hidden[0]]  (optional; needed by gcb200_tp_mlp_execute)
+ * batch must be a multiple of 128 and of 32 x world; every width a multiple of 8 x world.
+ *
+ * gcb200_tp_mlp_create     host only (no device needed): checks, fixes the tile configuration of the row-parallel layers.
+ * gcb200_tp_mlp_describe   text form of the step: layers, counters, arrivals expected per step.
+ * gcb200_tp_mlp_step       enqueues one step on `stream` for a device-resident input x [batch, hidden[0]] (the same
+ *                          values on every rank); *result = this rank's copy of the [batch, hidden[layers]] output, valid
+ *                          once the stream has run and until the step after the next.  The second call with the same
+ *                          x captures the step into a CUDA graph; later calls replay it.
+ * gcb200_tp_mlp_execute    the synchronous host-buffer form: this rank copies ITS row block of x_host (every rank
+ *                          passes the same full array) to the device, the blocks are exchanged over NVLink, the
+ *                          step runs, the whole result is copied to y_host (may be NULL on ranks that do not want
+ *                          it), and the call returns when all of it has finished.
+ * All ranks must issue the same sequence of steps; a rank that stops stepping makes the others' waits run out
+ * (GCB200_DEVICE_TIMEOUT from gcb200_device_error, GCB200_CUDA_ERROR from gcb200_tp_mlp_execute). */
+typedef struct gcb200_tp_mlp gcb200_tp_mlp;
+typedef struct {
+  int world, rank;
+  int64_t batch;
+  int layers;                    /* even, 2..12 */
+  const int64_t *hidden;         /* layers + 1 full widths */
+  const void *const *weights;    /* layers shards, bf16, device */
+  const void *const *biases;     /* layers entries, bf16, device; NULL = no bias */
+  int relu;
+  void *const *recv[2];
+  void *const *act[2];
+  void *const *signals;
+  void *const *x_in;             /* may be NULL */
+} gcb200_tp_mlp_desc;
+int gcb200_tp_mlp_create(const gcb200_tp_mlp_desc *desc, gcb200_tp_mlp **plan);
+int gcb200_tp_mlp_destroy(gcb200_tp_mlp *plan);
+int gcb200_tp_mlp_describe(const gcb200_tp_mlp *plan, int sm_count, char *buf, size_t cap, size_t *needed);
+int gcb200_tp_mlp_step(gcb200_tp_mlp *plan, const void *x, void *stream, void **result);
+int gcb200_tp_mlp_execute(gcb200_tp_mlp *plan, const void *x_host, void *y_host);
+
+/* Failure-path self-test: launches a kernel that waits (for at most `limit_cycles` SM clock cycles, which must not
+ * exceed the library's own limit) on a counter nothing ever adds to, gives up, records code 7 in the device error
+ * word and returns through its normal exit - the path every bounded wait of the kernels above takes when a peer or
+ * a copy never answers.  The reference maps such a run-time failure to dnnl_runtime_error
+ * (src/dnnl/dnnl_graph_compiler.cpp:217-225); the next dnnl_graph_compiler_execute on this device does the same once,
+ * clears the word and later calls succeed.  Nothing faults, traps or hangs. */
+int gcb200_wait_selftest(long long limit_cycles, void *stream);
+
+/* ---------------------------------------------------------------------------
  * Split-K bf16 matmul that allocates nothing.  No counterpart in the reference
  * (its runtime allocates freely from FILO pools); added for hosts that cannot
  * let a library call cudaMalloc once they are running — a server that has given

@@ -69,7 +69,10 @@ class _Cache:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    here = os.path.dirname(os.path.abspath(__file__))
+    ap.add_argument("--ref", default=os.environ.get("GC_REFERENCE_DIR") or
+                    os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference"),
+                    help="checkout of the reference (default: $GC_REFERENCE_DIR, else ../reference beside this repository)")
     a = ap.parse_args()
     sys.path.insert(0, os.path.join(a.ref, "test", "benchgc", "src"))
     sys.meta_path.insert(0, _StubFinder())

@@ -13,7 +13,10 @@ import pytest
 from gc_b200 import api, lib, partitions
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF_JSON = "/root/reference/test/dnnl/resources"
+# the reference checkout: GC_REFERENCE_DIR, else a directory named "reference" beside this repository; the test
+# that reads it is skipped where neither exists
+REF_JSON = os.path.join(os.environ.get("GC_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference"),
+                        "test", "dnnl", "resources")
 
 
 def test_library_exports_every_declared_symbol():
@@ -88,6 +91,43 @@ def test_error_classes_follow_the_reference_reader():
     assert _status(json.dumps(g)) == api.INVALID_GRAPH            # type mismatch for a produced value (:196-199)
     assert _status("{ not json") == api.INVALID_GRAPH
     assert _status("[]") == api.INVALID_GRAPH
+
+
+def test_malformed_post_ops_and_unwritable_outputs_are_refused_at_compile_time():
+    """A MatMul followed by an input-less ReLU or an output-less Add is a malformed graph, not a crash; an output
+    with non-dense strides, or an output that is one of the partition's own inputs, is refused (unimplemented)
+    instead of being returned unwritten."""
+    t = lambda i, s: {"id": i, "dtype": "bf16", "shape": s}
+    mm = {"kind": "MatMul", "inputs": [t(0, [32, 64]), t(1, [64, 48])], "outputs": [t(2, [32, 48])]}
+    env = lambda graph, **kw: json.dumps({"version": "3.5.0", "engine_kind": "cpu", "fpmath_mode": "strict", "graph": graph, **kw})
+    assert _status(env([mm, {"kind": "ReLU", "inputs": [], "outputs": [t(3, [32, 48])]}])) == api.INVALID_GRAPH
+    assert _status(env([mm, {"kind": "Add", "inputs": [t(2, [32, 48]), t(4, [48])], "outputs": []}])) == api.INVALID_GRAPH
+    relu = {"kind": "ReLU", "inputs": [t(2, [32, 48])], "outputs": [dict(t(3, [32, 48]), layout_type="strided", stride=[96, 2])]}
+    assert _status(env([mm, relu])) == api.UNIMPLEMENTED
+    relu["outputs"][0]["stride"] = [48, 1]                          # dense strides spelled out: fine
+    assert _status(env([mm, relu])) == api.SUCCESS
+    assert _status(env([mm], input_ports=[0, 1], output_ports=[2, 0])) == api.UNIMPLEMENTED   # output 0 is an input
+
+
+def test_column_sum_scratch_is_not_shared_with_other_temporaries():
+    """The zero-point column sums of a QuantizedMatMul are kept from one call to the next (constant weights), so
+    the planner must not hand their region to a later temporary of the same partition."""
+    t = lambda i, d, s, c=False: dict({"id": i, "dtype": d, "shape": s}, **({"property_type": "constant"} if c else {}))
+    M, N, K = 64, 128, 64
+    graph = [
+        {"kind": "QuantizedMatMul", "attrs": {"src_zp": {"type": "s64", "value": 128}},
+         "inputs": [t(0, "u8", [M, K]), t(1, "s8", [K, N], True), t(2, "f32", [N], True)], "outputs": [t(3, "f32", [M, N])]},
+        {"kind": "Sigmoid", "inputs": [t(3, "f32", [M, N])], "outputs": [t(4, "f32", [M, N])]},
+        {"kind": "Multiply", "inputs": [t(3, "f32", [M, N]), t(4, "f32", [M, N])], "outputs": [t(5, "f32", [M, N])]},
+        {"kind": "ReLU", "inputs": [t(5, "f32", [M, N])], "outputs": [t(6, "f32", [M, N])]},
+    ]
+    js = json.dumps({"version": "3.5.0", "engine_kind": "cpu", "fpmath_mode": "strict", "graph": graph})
+    plan = api.GraphCompiler().compile(js).plan()
+    # three f32 [M,N] temporaries (all live in the Multiply step) + the column sums (N * 4 bytes in a 1 KiB slot of
+    # their own): without the whole-partition lifetime the planner would put temporary 5 on top of the sums
+    assert "arena_bytes: %d" % (3 * M * N * 4 + 1024) in plan, plan
+    offs = sorted(int(m) for m in re.findall(r"@arena\+(\d+)", plan))
+    assert M * N * 4 not in offs and set(offs) == {0, M * N * 4 + 1024, 2 * M * N * 4 + 1024}, plan
 
 
 def test_mpl_graph_structure():

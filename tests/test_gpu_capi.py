@@ -194,6 +194,37 @@ def test_quantized_matmul_partition_bit_exact():
         assert np.array_equal(acc, wacc) and np.array_equal(out, wout)
 
 
+def test_quantized_matmul_keeps_its_column_sums_across_calls_and_steps():
+    """Device activations, constant host weights, and two temporaries after the matmul: the second call skips the
+    column-sum kernel (the weights are resident), so the sums must have survived the first call's later steps."""
+    import json
+
+    M, N, K = 256, 512, 384
+    g = torch.Generator().manual_seed(9)
+    A = torch.randint(0, 256, (M, K), generator=g, dtype=torch.uint8)
+    W = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8)
+    scale = (torch.rand(N, generator=g) * 0.009 + 0.001)
+    t = lambda i, d, s, c=False: dict({"id": i, "dtype": d, "shape": s}, **({"property_type": "constant"} if c else {}))
+    graph = [
+        {"kind": "QuantizedMatMul", "attrs": {"src_zp": {"type": "s64", "value": 128}},
+         "inputs": [t(0, "u8", [M, K]), t(1, "s8", [K, N], True), t(2, "f32", [N], True)], "outputs": [t(3, "f32", [M, N])]},
+        {"kind": "Sigmoid", "inputs": [t(3, "f32", [M, N])], "outputs": [t(4, "f32", [M, N])]},
+        {"kind": "Multiply", "inputs": [t(3, "f32", [M, N]), t(4, "f32", [M, N])], "outputs": [t(5, "f32", [M, N])]},
+    ]
+    js = json.dumps({"version": "3.5.0", "engine_kind": "cpu", "fpmath_mode": "strict", "graph": graph})
+    exe = api.GraphCompiler().compile(js)
+    _, deq = oracle.linear_u8s8(A.numpy(), W.numpy(), scale.numpy(), None, zp_a=128)
+    x = torch.from_numpy(deq)
+    sig = 1.0 / (1.0 + torch.exp(-x))
+    want = (x * sig).numpy()
+    Ad = A.cuda()
+    out = torch.empty(M, N, device="cuda")
+    for call in range(3):
+        out.zero_()
+        exe.execute({0: Ad, 1: W.numpy(), 2: scale.numpy()}, {5: out})
+        np.testing.assert_allclose(out.cpu().numpy(), want, rtol=2e-6, atol=1e-6, err_msg=f"call {call}")
+
+
 def test_mlp_chain_full_size_rows_against_oracle():
     """BASELINE configs[2]: 512 x (4096 -> 16384 -> 4096 -> 16384 -> 4096), N(0,0.02) weights, zero biases.
     Rows of the batch are independent, so the oracle recomputes a 16-row subset of the full-size run."""

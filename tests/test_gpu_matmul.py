@@ -74,12 +74,28 @@ def test_forced_tile_configurations_agree():
     want, acc = oracle.linear_bf16(tbits(A), tbits(B), tbits(b), relu=True, return_acc=True)
     Ad, Bd, bd = A.to(DEV), B.to(DEV), b.to(DEV)
     for swapped, bn, splits, stages, gm in [(0, 256, 1, 4, 8), (0, 128, 1, 6, 1), (0, 64, 1, 8, 3), (0, 256, 4, 2, 8),
-                                            (0, 128, 16, 3, 2), (0, 192, 1, 3, 8)]:
+                                            (0, 128, 16, 3, 2), (0, 192, 1, 3, 8),
+                                            # widths that are not a whole number of 64-column slabs: the last 16, 32 or
+                                            # 48 columns of every tile take the register-store tail of the epilogue
+                                            (0, 224, 1, 4, 8), (0, 240, 2, 3, 8), (0, 112, 1, 4, 2), (0, 80, 1, 4, 8),
+                                            (0, 208, 4, 3, 1), (0, 176, 1, 4, 8)]:
         cfg = lib.MatmulConfig(swapped, bn, splits, stages, gm, 0)
         Y = lib.matmul_bf16(Ad, Bd, bd, relu=True, cfg=cfg)
         torch.cuda.synchronize()
         _no_device_error()
         assert_bf16_close(tbits(Y), want, K, what=repr(cfg), pre=acc)
+        if bn % 128 == 0:
+            # the same tile on a CTA pair (256 x bn over two SMs): same MMAs in the same order per output element
+            cfg2 = lib.MatmulConfig(swapped, bn, splits, stages, gm, 0, 1, 0)
+            Y2 = lib.matmul_bf16(Ad, Bd, bd, relu=True, cfg=cfg2)
+            torch.cuda.synchronize()
+            _no_device_error()
+            assert torch.equal(Y2, Y), repr(cfg2)
+        # K-major weights ([N, K]) walk the same tiles through the other operand layout
+        Yt = lib.matmul_bf16(Ad, Bd.t().contiguous(), bd, relu=True, transpose_b=True, cfg=cfg)
+        torch.cuda.synchronize()
+        _no_device_error()
+        assert torch.equal(Yt, Y), repr(cfg)
 
 
 def test_f32out_and_reduce_epilogue_match_k_split_rule():
@@ -154,6 +170,25 @@ def test_full_size_gemm_rows_against_oracle():
     Bi = torch.randint(-2, 3, (4096, 2048), generator=torch.Generator().manual_seed(2)).bfloat16().to(DEV)
     Yi = lib.matmul_bf16(Ai, Bi)
     assert torch.equal(Yi.float(), (Ai.float() @ Bi.float()).bfloat16().float())
+
+
+@pytest.mark.parametrize("n,rows", [(2048, 64), (4096, 48), (16384, 24)])
+def test_gemm_sweep_sizes_rows_against_oracle(n, rows):
+    """BASELINE configs[4] at 2048^3, 4096^3 and 16384^3 (with 1024^3 and 8192^3 above, the whole square sweep):
+    a random subset of output rows recomputed by the oracle, spread so that the first and the last tile row,
+    the last wave and (at 16384^3: 2^28 outputs, 512 MiB per operand) the largest offsets are all hit."""
+    A, B = _rand_bf16((n, n), 20 + n % 7).to(DEV), _rand_bf16((n, n), 21 + n % 5).to(DEV)
+    Y = lib.matmul_bf16(A, B)
+    torch.cuda.synchronize()
+    _no_device_error()
+    pick = torch.randperm(n, generator=torch.Generator().manual_seed(n))[: rows - 2]
+    idx = torch.cat([torch.tensor([0, n - 1]), pick]).unique().sort().values
+    want = oracle.linear_bf16(tbits(A[idx]), tbits(B))
+    mx, same = assert_bf16_close(tbits(Y[idx]), want, n, what=f"{n}^3 row subset")
+    print(f"gemm {n}^3, {len(idx)} rows: max_abs={mx:.4g} bit-identical={same:.5f}")
+    assert same > 0.99
+    # every output was written (no tile skipped): the finite, non-zero check costs one pass on the device
+    assert bool(torch.isfinite(Y.float()).all()) and int((Y == 0).sum()) < n
 
 
 def test_decode_shape_against_oracle():

@@ -69,6 +69,96 @@ def _worker(rank, world, port, mode, q):
         dist.destroy_process_group()
 
 
+def _fused_worker(rank, world, port, full, q):
+    """The tensor-parallel step behind the C ABI (gcb200_tp_mlp_*): device-resident steps (eager, captured, replayed)
+    and the host-buffer form, on the small chain or on BASELINE configs[2] at full size."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    from gc_b200 import lib
+    from gc_b200.tensor_parallel import FusedTensorParallelMLP, shard_weights
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        X, Ws, Bs, batch, hidden = _make_full() if full else (*_make(), BATCH, HIDDEN)
+        ws, bs = shard_weights([w.to(dev) for w in Ws], [b.to(dev) for b in Bs], world, rank)
+        tp = FusedTensorParallelMLP(ws, bs, batch, hidden, dev, relu=True)
+        Xd = X.to(dev)
+        outs = []
+        for _ in range(4):                     # eager, captured, replayed, replayed: counters and buffers carry over
+            y = tp.step(Xd)
+            torch.cuda.synchronize()
+            outs.append(_bits(y).copy())
+        assert lib.device_error() == 0
+        xh, yh = X.pin_memory(), torch.empty(batch, hidden[-1], dtype=torch.bfloat16).pin_memory()
+        for _ in range(3):                     # the synchronous host-buffer form, every rank reading the result
+            yh.zero_()
+            tp.execute(xh, yh)
+            outs.append(_bits(yh).copy())
+        assert lib.device_error() == 0
+        dist.barrier()
+        tp.close()
+        rows = slice(None) if not full else FULL_ROWS
+        q.put((rank, [o[rows] for o in outs]))
+    finally:
+        dist.destroy_process_group()
+
+
+FULL_ROWS = [0, 1, 63, 64, 127, 128, 129, 255, 256, 300, 383, 384, 447, 448, 510, 511]
+
+
+def _make_full():
+    from gc_b200 import benchgc_compat as bc
+
+    hidden = (4096, 16384, 4096, 16384, 4096)
+    X = bc.fill_tensor((512, hidden[0]), "bf16", "N", (0, 1), 0)
+    Ws = [bc.fill_tensor((hidden[i], hidden[i + 1]), "bf16", "N", (0, 0.02), 1 + i) for i in range(4)]
+    Bs = [torch.zeros(hidden[i + 1], dtype=torch.bfloat16) for i in range(4)]
+    return X, Ws, Bs, 512, hidden
+
+
+@pytest.mark.parametrize("full", [False, True])
+def test_fused_tensor_parallel_step_behind_the_c_abi(full):
+    """Every hand-off between the GPUs is a device counter of this library's own kernels.  Small chain: the whole
+    result against the oracle; BASELINE configs[2] at full size (512 x 4096-16384-4096-16384-4096): 16 rows against
+    the oracle.  Every rank, every step (device-resident and host-buffer form): identical bits."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    if world == 3:
+        world = 2
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fused_worker, args=(r, world, port, full, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=600) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for r in range(world):
+        for step in range(len(res[r])):
+            assert np.array_equal(res[r][step], res[0][0]), (r, step)
+    if full:
+        X, Ws, Bs, _, hidden = _make_full()
+        h = _bits(X)[FULL_ROWS]
+        for W, b in zip(Ws, Bs):
+            h = oracle.linear_bf16(h, _bits(W), _bits(b), relu=True)
+        mx, same = assert_bf16_close(res[0][0], h, 16384, what="fused tp, configs[2] full size", floor_div=1.0)
+    else:
+        X, Ws, Bs = _make()
+        want = oracle.mlp_bf16(_bits(X), [_bits(w) for w in Ws], [_bits(b) for b in Bs], relu=True)
+        from _util import bf16_f32
+        pre = np.abs(bf16_f32(want)) + np.abs(bf16_f32(_bits(Bs[3])))[None, :]
+        mx, same = assert_bf16_close(res[0][0], want, max(HIDDEN), what="fused tp", floor_div=1.0, pre=pre)
+    print(f"tp{world} fused counters full={full}: max_abs={mx:.4g} bit-identical={same:.5f}")
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -10,6 +10,7 @@ import ctypes as C
 import pytest
 import torch
 
+import oracle
 from _util import assert_bf16_close, tbits
 from gc_b200 import lib
 
@@ -45,6 +46,10 @@ def test_static_scratch_matmul_matches_existing_entry_point_twice():
             acc = A.float() @ B.float()
             mx, same = assert_bf16_close(tbits(Y), tbits(want), K, what=f"static {M}x{N}x{K} call {call}", pre=acc.cpu().numpy())
             assert same > 0.99
+            # and against the CPU oracle of the reference's arithmetic, like every other parity test
+            want_o, acc_o = oracle.linear_bf16(tbits(A), tbits(B), tbits(bias), relu=True, return_acc=True)
+            mx_o, same_o = assert_bf16_close(tbits(Y), want_o, K, what=f"static {M}x{N}x{K} call {call} vs oracle", pre=acc_o)
+            assert same_o > 0.99
             if splits > 0:
                 # with the same split count the two paths add the same planes in the same order
                 cfg = lib.select_matmul_config(M, N, K, 2, 4, lib.sm_count())
@@ -61,3 +66,8 @@ def test_static_scratch_rejects_oversized_requests():
     assert st == 1
     msg = lib.load().gcb200_last_error().decode()
     assert "exceeds the static scratch" in msg and "16777216" in msg
+    # sizes whose byte count would wrap 64 bits are refused as well, not truncated (no memory is touched: the
+    # check comes before any launch)
+    st = lib.load().gcb200_matmul_bf16_splitk_static(A.data_ptr(), B.data_ptr(), None, A.data_ptr(), 1 << 40, 1 << 24, 64, 1, 0,
+                                                     C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 1
