@@ -463,6 +463,39 @@ def run_sharded_case(spec: str, steps: int, warmup: int, rank: int, world: int):
             "timing": "CUDA events, max over ranks, inputs resident"}
 
 
+PARITY_ROWS = [0, 1, 63, 64, 127, 128, 129, 255, 256, 300, 383, 384, 447, 448, 510, 511]
+
+
+def parity_rows(y_dev, X_host, W_host, B_host):
+    """16 rows of the MLP output the timed step left on the device, against the CPU oracle fed the same rows (rows of a
+    batch are independent).  Tolerance of the chain test: |diff| <= 1e-2 max(|want|, rms).  The oracle is used here as
+    a checker only."""
+    import numpy as np
+    import torch
+
+    import oracle
+
+    def bits(t):
+        return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))
+    idx = torch.tensor(PARITY_ROWS)
+    h = bits(X_host[idx])
+    for W, b in zip(W_host, B_host):
+        h = oracle.linear_bf16(h, bits(W), bits(b), relu=True)
+    want = oracle.bf16_to_f32(h).astype(np.float64)
+    got = oracle.bf16_to_f32(bits(y_dev[idx.to(y_dev.device)])).astype(np.float64)
+    rms = float(np.sqrt(np.mean(want[want != 0] ** 2))) if (want != 0).any() else 0.0
+    diff = np.abs(got - want)
+    ok = bool((diff <= 1e-2 * np.maximum(np.abs(want), rms)).all())
+    return {"rows": len(PARITY_ROWS), "max_abs": float(diff.max()), "bit_identical": float((got == want).mean()), "ok": ok,
+            "rule": "|diff| <= 1e-2 max(|want|, rms) against the CPU oracle"}
+
+
+SHARDED = ["gemm:8192:8192:8192", "gemm:16384:16384:16384", "decode", "int8:1024:4096:4096", "attention:16:32:2048:128:0",
+           "attention:16:32:2048:128:1"]
+
+
 def parallelism_of(world: int) -> str:
     """How the workload is spread over `world` GPUs: a function of the launch alone, so that the reference arm
     (which runs on the host) and this arm print the same `config`."""
@@ -578,6 +611,27 @@ def main():
             bound.run()   # dnnl_graph_compiler_execute: H2D of X, 4 launches, D2H of the result, synchronous
 
         parallelism = "single GPU"
+    elif os.environ.get("GC_B200_EXCHANGE", "fused_counters") == "fused_counters":
+        # The tensor-parallel step behind the C ABI (gcb200_tp_mlp_*): GEMMs, exchange and every hand-off between the
+        # GPUs are this library's own kernels; the step is replayed as a CUDA graph inside the library.
+        from gc_b200.tensor_parallel import FusedTensorParallelMLP
+
+        ws, bs = shard_weights([w.to(dev) for w in W_host], [b.to(dev) for b in B_host], world, rank)
+        tpf = FusedTensorParallelMLP(ws, bs, BATCH, HIDDEN, dev, relu=True)
+        Xd = X_host.to(dev)
+        holder = {}
+
+        def step_device():
+            holder["y"] = tpf.step(Xd)
+
+        def step_e2e():
+            # gcb200_tp_mlp_execute: each rank copies its row block of the input over its own PCIe link, the blocks
+            # cross NVLink, the step runs, rank 0 reads the whole result back; returns when all of it has finished
+            holder["y"] = tpf.execute(X_host, out_host if rank == 0 else None)
+
+        parallelism = (f"tp{world} behind the C ABI: row-parallel partial sums leave the GEMM epilogue for the rank that owns the rows "
+                       "(peer stores), the owner reduces and stores the bf16 rows to every rank; hand-offs are device counters of "
+                       "this library's kernels; one CUDA-graph replay per step")
     else:
         from gc_b200.tensor_parallel import AllReduceExchange, CudaOps, PeerPushExchange, PeerReduceScatterExchange
 
@@ -679,7 +733,7 @@ def main():
         en.record()
         barrier()
         launches = lib.launch_count() - l0
-        if world > 1:   # kernels launched by graph replays are not seen by the library's host-side counter
+        if world > 1:   # kernels launched by torch graph replays are not seen by the library's host-side counter
             launches += (holder.get("replays", 0) - r0) * holder.get("launches_per_replay", 0)
         ms = st.elapsed_time(en)
         clocks = sampler   # still running: it also covers the end-to-end region that follows and is stopped there
@@ -694,6 +748,10 @@ def main():
     clocks = sampler.stop()   # sampled from the start of the device-timed region to the end of the end-to-end one
     assert lib.device_error() == 0, "a kernel reported a bounded-wait time-out"
 
+    # ---- the step that was timed computed the right thing: 16 rows of its output against the CPU oracle (rank 0)
+    parity = None
+    if rank == 0:
+        parity = parity_rows(outd if world == 1 else holder["y"], X_host, W_host, B_host)
     peaks = measured_peaks()
     gemm_launches = launches  # every launch in the timed region is one of this library's kernels
     per_launch_ms = ms_dev * a.steps / max(launches, 1)
@@ -717,6 +775,7 @@ def main():
                         "per step: H2D of the activations on every rank, the tensor-parallel step, D2H of the result on rank 0"},
         "gpu_launches": int(gemm_launches),
         "exchange": exchange_note,
+        "parity": parity,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s", "frac": achieved / peaks[peak_kind],
                      "traffic": traffic, "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind}",
@@ -732,6 +791,17 @@ def main():
             line["cpu_onednn_class"] = {"error": repr(e)[:100]}
     if a.sweep and world == 1:
         line["sweep"] = [run_case(c, 10 if "16384" in c else 20, 3, library=True) for c in SWEEP]
+    if a.sweep and world > 1:
+        # the other configs that shard, at this number of ranks (strong scaling; the 1-GPU figures are in the N=1 line's sweep)
+        if "tpf" in locals():
+            tpf.close()
+        sharded = []
+        for c in SHARDED:
+            try:
+                sharded.append(run_sharded_case(c, 5 if "16384" in c else 10, 3, rank, world))
+            except Exception as e:   # one case must not take the line down
+                sharded.append({"case": c, "error": f"{type(e).__name__}: {e}"[:200]})
+        line["sharded"] = sharded
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

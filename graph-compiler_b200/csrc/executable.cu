@@ -12,6 +12,7 @@
 #include <memory>
 #include <mutex>
 #include <new>
+#include <sstream>
 #include <string>
 #include <vector>
 
@@ -21,6 +22,7 @@
 #include "../../include/gc_b200.h"
 #include "attention.h"
 #include "graph.h"
+#include "log.h"
 #include "memplan.h"
 #include "runtime.h"
 #include "sm100_ptx.cuh"
@@ -40,7 +42,7 @@ struct EwParams {
   long long dims[kMaxRank];   // output dims
   long long sa[kMaxRank];     // element strides of operand a per output dim (0 = broadcast)
   long long sb[kMaxRank];
-  int fn;                     // binary: 0 add 1 sub 2 mul 3 div; unary: 0 relu 1 sigmoid 2 pow 3 cast
+  int fn;                     // binary: 0 add 1 sub 2 mul 3 div; unary: 0 relu 1 sigmoid 2 pow 3 cast 4 exp 5 negate
   float beta;
   int dt_a, dt_b, dt_o;       // 0 f32, 1 bf16, 2 f16
   // how an operand's offset follows from the flat output index i without walking the dims:
@@ -111,6 +113,8 @@ __global__ void unary_kernel(EwParams p, const void *a, void *o) {
       else if (p.beta == 3.f) v = __fmul_rn(__fmul_rn(x, x), x);
       else v = powf(x, p.beta);
       break;
+    case 4: v = expf(x); break;
+    case 5: v = -x; break;
     default: v = x; break;
     }
     ew_store(o, i, p.dt_o, v);
@@ -269,6 +273,7 @@ struct dnnl_graph_compiler_executable {
   mutable DeviceBuffer arena;
   mutable std::vector<DeviceBuffer> in_stage, out_stage;
   mutable std::vector<char> comp_ready; // per QMATMUL scratch: column sums computed for a cached constant weight
+  static constexpr int kCanary = 0xA5;
   mutable DeviceBuffer splitk;          // split-K partial planes of this executable's matmul steps (they run one after
                                         // another on one stream, so one block sized for the largest request serves all)
 
@@ -299,6 +304,9 @@ struct dnnl_graph_compiler_executable {
     }
     GCB_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&host_code), sizeof(int), cudaHostAllocDefault));
     if (plan.arena_bytes) arena.reserve(plan.arena_bytes);
+    if (plan.guard_bytes && plan.arena_bytes) GCB_CUDA(cudaMemset(arena.ptr, kCanary, plan.arena_bytes));
+    gcLogD("executable prepared on device ", device, ": arena ", plan.arena_bytes, " bytes, ", plan.steps.size(), " steps, guard bands ",
+           plan.guard_bytes, " bytes");
     in_stage.resize(plan.part.input_ids.size());
     out_stage.resize(plan.part.output_ids.size());
     comp_ready.assign(plan.scratch.size(), 0);
@@ -366,6 +374,54 @@ struct dnnl_graph_compiler_executable {
     m.bias_kind = bias ? BIAS_BF16 : BIAS_NONE; m.bias = bias; m.relu = st.relu;
     m.scratch = splitk.ptr; m.scratch_bytes = splitk.bytes;
     matmul_tc(m, s);
+  }
+
+  // Debug mode: every guard band must still hold the canary.  Returns the number of damaged bands and describes
+  // the first one; reads the bands back to the host (slow, debug only).  The stream must be idle.
+  int check_guards(std::string *what) const {
+    if (!plan.guard_bytes || !arena.ptr) return 0;
+    std::vector<unsigned char> h(plan.guard_bytes);
+    int bad = 0;
+    for (const auto &band : plan.guards) {
+      GCB_CUDA(cudaMemcpy(h.data(), static_cast<const uint8_t *>(arena.ptr) + band.first, plan.guard_bytes, cudaMemcpyDeviceToHost));
+      size_t first_bad = plan.guard_bytes;
+      for (size_t i = 0; i < plan.guard_bytes; ++i)
+        if (h[i] != kCanary) { first_bad = i; break; }
+      if (first_bad == plan.guard_bytes) continue;
+      if (bad++ == 0 && what)
+        *what = "guard band at arena offset " + std::to_string(band.first) + " (" +
+                (band.second == ~size_t(0) ? std::string("scratch slot") : "tensor " + std::to_string(band.second)) +
+                ") overwritten at byte " + std::to_string(first_bad);
+    }
+    return bad;
+  }
+
+  // One line per step with the kernel and, for matmuls, the tile configuration the selector gives for `sm_count` SMs.
+  std::string describe_launches(int sm_count) const {
+    std::ostringstream os;
+    for (size_t i = 0; i < plan.steps.size(); ++i) {
+      const Step &st = plan.steps[i];
+      os << "  step " << i << " " << st.op << ": ";
+      if (st.kind == StepKind::MATMUL || st.kind == StepKind::QMATMUL) {
+        const bool q = st.kind == StepKind::QMATMUL;
+        const bool bf16 = q || plan.part.tensors.at(st.in[0]).dtype == DType::BF16;
+        const bool tma = ((st.trans_a ? st.M : st.K) * (q ? 1 : 2)) % 16 == 0 && ((st.trans_b ? st.K : st.N) * (q ? 1 : 2)) % 16 == 0;
+        if (!bf16 || !tma) {
+          os << "matmul_simt_kernel (exact-order f32) " << st.M << "x" << st.N << "x" << st.K << "\n";
+          continue;
+        }
+        const MatmulConfig c = select_matmul_config(st.M, st.N, st.K, q ? 1 : 2, q ? 4 : 2, sm_count);
+        os << "gemm_kernel<" << (q ? "u8 x s8" : "bf16") << (c.swapped ? ", weights on the MMA M side" : "") << "> " << st.M << "x" << st.N
+           << "x" << st.K << " tile 128x" << c.bn << " splits " << c.splits << " stages " << c.stages << " K blocks/stage "
+           << std::max(1, c.kpb) << " grid " << c.grid << (c.splits > 1 ? " + reduce_planes" : "") << (q ? " + colsum_s8" : "") << "\n";
+      } else if (st.kind == StepKind::SDPA) {
+        os << "attention_kernel B*H=" << st.batch * st.heads << " S=" << st.seq << " D=" << st.dim << " causal=" << st.causal << "\n";
+      } else {
+        os << (st.kind == StepKind::REDUCE ? "reduce kernel" : st.kind == StepKind::BINARY ? "binary_kernel"
+               : st.kind == StepKind::COPY ? "device-to-device copy" : "unary_kernel") << "\n";
+      }
+    }
+    return os.str();
   }
 
   // own_stream: run on the executable's private stream (the synchronous C API); otherwise on
@@ -576,7 +632,17 @@ struct dnnl_graph_compiler_executable {
       const int code = *host_code;
       if (code) {
         GCB_CUDA(cudaMemset(device_state().d_error, 0, sizeof(int)));
+        gcLogE("device error word = ", code, " after execute");
         throw std::runtime_error("a kernel gave up a bounded wait (code " + std::to_string(code) + ")");
+      }
+      if (plan.guard_bytes) {
+        std::string what;
+        const int bad = check_guards(&what);
+        if (bad) {
+          GCB_CUDA(cudaMemset(arena.ptr, kCanary, plan.arena_bytes));   // re-arm: temporaries are rewritten by every call
+          gcLogE(bad, " guard band(s) damaged: ", what);
+          throw std::runtime_error(what);
+        }
       }
     }
   }
@@ -736,6 +802,13 @@ struct dnnl_graph_compiler_executable {
       count_launch();
       break;
     }
+    case StepKind::COPY: {
+      const LogicalTensor &A = p.tensors.at(st.in[0]);
+      if (!is_dense(A)) throw std::logic_error("StaticReshape of a strided tensor");
+      const size_t bytes = size_t(A.numel()) * dtype_bytes(A.dtype);
+      if (bytes) GCB_CUDA(cudaMemcpyAsync(addr(st.out[0]), addr(st.in[0]), bytes, cudaMemcpyDeviceToDevice, s));
+      break;
+    }
     default: throw std::logic_error("unsupported step");
     }
     (void)in_ptr;
@@ -776,7 +849,10 @@ GCB_EXPORT dnnl_status_t dnnl_graph_compiler_compile(const dnnl_graph_compiler *
   (void)gc;
   try {
     if (!graph_json || !exe) throw std::invalid_argument("null argument");
-    *exe = new dnnl_graph_compiler_executable(std::string(graph_json));
+    auto *e = new dnnl_graph_compiler_executable(std::string(graph_json));
+    *exe = e;
+    gcLogD("compiled a partition of ", e->plan.part.ops.size(), " ops into ", e->plan.steps.size(), " steps");
+    if (gcb::logging::verbose()) std::cout << "[gc_b200] launch plan\n" << e->describe_launches(148) << std::flush;
     return dnnl_success;
   } catch (const std::invalid_argument &e) {
     g_last_error = e.what();
@@ -806,6 +882,7 @@ static dnnl_status_t execute_impl(const dnnl_graph_compiler_executable *exe, dnn
     return dnnl_out_of_memory;
   } catch (const std::exception &e) {
     g_last_error = e.what();
+    gcLogE("execute failed: ", e.what());
     return dnnl_runtime_error; // the reference maps every execute failure to runtime_error (:217-225)
   } catch (...) {
     return dnnl_runtime_error;
@@ -834,6 +911,51 @@ GCB_EXPORT int gcb200_plan_dump(const dnnl_graph_compiler_executable *exe, char 
     buf[n] = '\0';
   }
   return GCB200_OK;
+}
+
+GCB_EXPORT int gcb200_describe_launches(const dnnl_graph_compiler_executable *exe, int sm_count, char *buf, size_t cap, size_t *needed) {
+  if (!exe) return GCB200_INVALID_ARGUMENT;
+  const std::string s = exe->describe_launches(sm_count > 0 ? sm_count : 148);
+  if (needed) *needed = s.size() + 1;
+  if (buf && cap) {
+    const size_t n = std::min(cap - 1, s.size());
+    std::memcpy(buf, s.data(), n);
+    buf[n] = '\0';
+  }
+  return GCB200_OK;
+}
+
+GCB_EXPORT int gcb200_guard_check(const dnnl_graph_compiler_executable *exe, int *damaged) {
+  if (!exe || !damaged) return GCB200_INVALID_ARGUMENT;
+  try {
+    std::lock_guard<std::mutex> g(exe->mu);
+    if (exe->ready) GCB_CUDA(cudaDeviceSynchronize());
+    std::string what;
+    *damaged = exe->check_guards(&what);
+    if (*damaged) g_last_error = what;
+    return GCB200_OK;
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+    return GCB200_CUDA_ERROR;
+  }
+}
+
+GCB_EXPORT int gcb200_guard_selftest(const dnnl_graph_compiler_executable *exe) {
+  if (!exe) return GCB200_INVALID_ARGUMENT;
+  try {
+    std::lock_guard<std::mutex> g(exe->mu);
+    if (!exe->plan.guard_bytes || exe->plan.guards.empty()) throw std::invalid_argument("the partition was not compiled with GC_B200_GUARD");
+    exe->prepare();
+    // what an out-of-bounds store of a kernel would do: one byte of the first band loses its canary
+    GCB_CUDA(cudaMemset(static_cast<uint8_t *>(exe->arena.ptr) + exe->plan.guards.front().first + 3, 0, 1));
+    return GCB200_OK;
+  } catch (const std::invalid_argument &e) {
+    g_last_error = e.what();
+    return GCB200_INVALID_ARGUMENT;
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+    return GCB200_CUDA_ERROR;
+  }
 }
 
 GCB_EXPORT int gcb200_schedule_memory(const uint64_t *trace_buffer, const uint64_t *trace_size, int n_traces,

@@ -2,6 +2,7 @@
 #include "memplan.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <limits>
 #include <map>
 #include <set>
@@ -64,11 +65,13 @@ const std::map<std::string, DType> kDTypes = {
     {"s8", DType::S8},           {"u8", DType::U8},           {"f64", DType::F64},   {"boolean", DType::BOOLEAN},
     {"f8_e5m2", DType::F8_E5M2}, {"f8_e4m3", DType::F8_E4M3}, {"s4", DType::S4},     {"u4", DType::U4}};
 
-// The eleven kinds of the reference (src/dnnl/JsonParser.h:152-164) plus the two
-// extension kinds this backend adds for partitions the reference front end
-// cannot express.
+// The eleven kinds of the reference (src/dnnl/JsonParser.h:152-164) plus the extension kinds this backend
+// adds: the two partitions the reference front end cannot express (int8 matmul with dequantisation, fused
+// attention) and three small ops that the linalg form of the reference's own llama2 case needs when it is
+// lowered to a partition (test/benchgc/cases/llama2.mlir: tensor.collapse/expand_shape, linalg.exp, linalg.negf).
 const std::set<std::string> kKinds = {"Add",     "Divide",  "MatMul",   "Multiply", "Pow",           "ReduceMean", "ReduceSum",
-                                      "ReLU",    "Sigmoid", "Subtract", "Typecast", "QuantizedMatMul", "SDPA"};
+                                      "ReLU",    "Sigmoid", "Subtract", "Typecast", "QuantizedMatMul", "SDPA",
+                                      "StaticReshape", "Exp", "Negate"};
 
 const std::string &as_string(const JsonValue &v, const char *what) {
   if (v.kind != JsonValue::String) invalid(std::string("string expected for ") + what);
@@ -407,10 +410,17 @@ Plan build_plan(Partition part) {
       st.fn = op.kind == "Add" ? 0 : op.kind == "Subtract" ? 1 : op.kind == "Multiply" ? 2 : 3;
       for (auto &t : op.inputs)
         if (!is_float(t.dtype)) unsupported(op.kind + " supports float tensors");
-    } else if (op.kind == "ReLU" || op.kind == "Sigmoid" || op.kind == "Pow" || op.kind == "Typecast") {
+    } else if (op.kind == "StaticReshape") {
+      // same elements, another shape (tensor.collapse_shape / expand_shape of the linalg form): a device copy
+      if (op.inputs.size() != 1 || op.outputs.size() != 1) invalid("StaticReshape expects 1 input and 1 output");
+      if (op.inputs[0].numel() != op.outputs[0].numel() || op.inputs[0].dtype != op.outputs[0].dtype)
+        invalid("StaticReshape must keep the element count and the dtype");
+      st.kind = StepKind::COPY;
+    } else if (op.kind == "ReLU" || op.kind == "Sigmoid" || op.kind == "Pow" || op.kind == "Typecast" || op.kind == "Exp" ||
+               op.kind == "Negate") {
       if (op.inputs.size() != 1 || op.outputs.size() != 1) invalid(op.kind + " expects 1 input and 1 output");
       st.kind = StepKind::UNARY;
-      st.fn = op.kind == "ReLU" ? 0 : op.kind == "Sigmoid" ? 1 : op.kind == "Pow" ? 2 : 3;
+      st.fn = op.kind == "ReLU" ? 0 : op.kind == "Sigmoid" ? 1 : op.kind == "Pow" ? 2 : op.kind == "Typecast" ? 3 : op.kind == "Exp" ? 4 : 5;
       if (op.kind == "Pow") {
         const AttrValue *b = op.attr("beta");
         if (!b) invalid("Pow needs attribute beta");
@@ -436,6 +446,12 @@ Plan build_plan(Partition part) {
   }
 
   // ---- storage: arguments and results are the caller's; everything else lives in the arena
+  size_t guard = 0;
+  if (const char *g = std::getenv("GC_B200_GUARD")) {
+    const long v = std::atol(g);
+    if (v > 0) guard = (size_t(std::min<long>(v, 1 << 20)) + 255) / 256 * 256;   // whole 256-byte units keep slices TMA-aligned
+  }
+  plan.guard_bytes = guard;
   std::vector<BufferLife> lives;
   std::vector<size_t> live_ids;
   std::unordered_map<size_t, size_t> live_index;
@@ -454,7 +470,7 @@ Plan build_plan(Partition part) {
       if (li == live_index.end()) {
         live_index[id] = lives.size();
         live_ids.push_back(id);
-        lives.push_back(BufferLife{bytes, step, step});
+        lives.push_back(BufferLife{bytes + 2 * guard, step, step});
         plan.slots[id] = TensorSlot{TensorSlot::ARENA, 0, 0, bytes};
       } else {
         lives[li->second].last = std::max(lives[li->second].last, step);
@@ -473,7 +489,7 @@ Plan build_plan(Partition part) {
       // The column sums of a constant weight are computed by the first call and kept for the following ones,
       // so their region must not be handed to any other temporary: it is live over every step (and, as the
       // arena belongs to the executable, from one call to the next).
-      lives.push_back(BufferLife{size_t(st.N) * 4, 0, int(plan.steps.size()) - 1});
+      lives.push_back(BufferLife{size_t(st.N) * 4 + 2 * guard, 0, int(plan.steps.size()) - 1});
     }
   }
   // an output may also be consumed by a later op.  Results are written densely: an output declared with
@@ -494,8 +510,19 @@ Plan build_plan(Partition part) {
   }
   std::vector<size_t> offsets;
   plan.arena_bytes = plan_arena(lives, 1024, offsets);
-  for (size_t i = 0; i < live_ids.size(); ++i) plan.slots[live_ids[i]].offset = offsets[live_index[live_ids[i]]];
-  for (size_t i = 0; i < scratch_reqs.size(); ++i) plan.scratch[i].offset = offsets[scratch_reqs[i].first];
+  for (size_t i = 0; i < live_ids.size(); ++i) plan.slots[live_ids[i]].offset = offsets[live_index[live_ids[i]]] + guard;
+  for (size_t i = 0; i < scratch_reqs.size(); ++i) plan.scratch[i].offset = offsets[scratch_reqs[i].first] + guard;
+  if (guard) {
+    for (size_t id : live_ids) {
+      const TensorSlot &sl = plan.slots[id];
+      plan.guards.emplace_back(sl.offset - guard, id);
+      plan.guards.emplace_back(sl.offset + sl.bytes, id);
+    }
+    for (const TensorSlot &sl : plan.scratch) {
+      plan.guards.emplace_back(sl.offset - guard, ~size_t(0));
+      plan.guards.emplace_back(sl.offset + sl.bytes, ~size_t(0));
+    }
+  }
   return plan;
 }
 
@@ -506,6 +533,7 @@ std::string Plan::dump() const {
   os << "\noutputs:";
   for (size_t id : part.output_ids) os << ' ' << id;
   os << "\narena_bytes: " << arena_bytes << "\n";
+  if (guard_bytes) os << "guard_bytes: " << guard_bytes << " (" << guards.size() << " bands)\n";
   auto where = [&](size_t id) {
     const TensorSlot &s = slots.at(id);
     std::ostringstream w;

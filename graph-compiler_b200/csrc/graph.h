@@ -83,7 +83,7 @@ struct Step {
   int64_t batch = 0, heads = 0, seq = 0, dim = 0;
   float scale = 1.f;
   bool causal = false;
-  // BINARY: 0 add 1 sub 2 mul 3 div ; UNARY: 0 relu 1 sigmoid 2 pow 3 typecast
+  // BINARY: 0 add 1 sub 2 mul 3 div ; UNARY: 0 relu 1 sigmoid 2 pow 3 typecast 4 exp 5 negate
   int fn = 0;
   float beta = 1.f;
   // REDUCE
@@ -97,6 +97,12 @@ struct Plan {
   std::unordered_map<size_t, TensorSlot> slots; // every tensor the steps touch
   std::vector<TensorSlot> scratch;              // per-step extra temporaries (arena)
   size_t arena_bytes = 0;
+  // Debug mode (GC_B200_GUARD=<bytes>, read when the partition is compiled): every arena slice is planned with this
+  // many bytes of canary before and after it; `guards` lists the bands as (arena offset, tensor id or ~0 for a
+  // scratch slot).  The counterpart of the canary the reference's debug memory pool keeps at the head of every
+  // allocation (lib/gc/ExecutionEngine/CPURuntime/MemoryPool.cpp:55-60, checked at :213-217).
+  size_t guard_bytes = 0;
+  std::vector<std::pair<size_t, size_t>> guards;
   std::string dump() const;                     // human-readable, stable (tests read it)
 };
 

@@ -228,7 +228,14 @@ MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byte
   const int kpb_eff = std::max(1, c.kpb);
   c.stages = int(std::min<size_t>(8, budget / ((a_bytes + b_bytes) * size_t(kpb_eff))));
   c.stages = std::max(2, std::min(c.stages, std::max(2, ceil_div(k_blocks, kpb_eff))));
-  c.group_m = 8;
+  // Rasterisation: 8 tile rows per column sweep; with very long K (measured at 16384^3: 6.34 ms against 6.92 ms) four,
+  // so that fewer CTAs walk the same weight columns and drift apart in L2.
+  c.group_m = (k_blocks >= 256 && tiles >= 8 * sm_count) ? 4 : 8;
+  // CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles on two SMs, half the weight bytes per SM): measured faster where
+  // a few hundred activation rows meet a large streamed weight matrix (512 x 16384 x 4096: 64.7 against 73.0 us;
+  // 512 x 4096 x 16384 split in two: 64.3 against 68.6 us), slower on large square shapes (4096^3: 109.5 against 103.1 us).
+  c.pair = (!c.swapped && dtype_bytes == 2 && c.bn == 256 && c.kpb <= 1 && M % 256 == 0 && M <= 1024 && N >= 2048 && N % 256 == 0 &&
+            k_blocks / std::max(1, c.splits) >= 16) ? 1 : 0;
   c.grid = std::min(tiles * c.splits, sm_count);
   if (const char *ov = std::getenv("GC_B200_TILE")) {
     // "bn,splits,stages,group_m" — any field may be 0 to keep the heuristic's choice

@@ -67,6 +67,12 @@ def _bind():
     l.gcb200_plan_arena.argtypes = [C.POINTER(C.c_int64), C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.c_int64,
                                     C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
     l.gcb200_plan_arena.restype = C.c_int
+    l.gcb200_describe_launches.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
+    l.gcb200_describe_launches.restype = C.c_int
+    l.gcb200_guard_check.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+    l.gcb200_guard_check.restype = C.c_int
+    l.gcb200_guard_selftest.argtypes = [C.c_void_p]
+    l.gcb200_guard_selftest.restype = C.c_int
     l._gc_api_bound = True
     return l
 
@@ -147,6 +153,28 @@ class Executable:
         buf = C.create_string_buffer(n.value)
         _bind().gcb200_plan_dump(self._h, buf, n.value, None)
         return buf.value.decode()
+
+    def launches(self, sm_count: int = 148) -> str:
+        """One line per step: kernel and, for matmuls, the tile configuration chosen for ``sm_count`` SMs."""
+        n = C.c_size_t(0)
+        _bind().gcb200_describe_launches(self._h, sm_count, None, 0, C.byref(n))
+        buf = C.create_string_buffer(n.value)
+        _bind().gcb200_describe_launches(self._h, sm_count, buf, n.value, None)
+        return buf.value.decode()
+
+    def guard_check(self) -> int:
+        """Damaged guard bands of the workspace arena (partitions compiled under GC_B200_GUARD); 0 = intact."""
+        n = C.c_int(-1)
+        st = _bind().gcb200_guard_check(self._h, C.byref(n))
+        if st != 0:
+            raise DnnlError(RUNTIME_ERROR, _lib.load().gcb200_last_error().decode(errors="replace"))
+        return n.value
+
+    def guard_selftest(self) -> None:
+        """Damages one guard band from the host (test hook for the detection)."""
+        st = _bind().gcb200_guard_selftest(self._h)
+        if st != 0:
+            raise DnnlError(RUNTIME_ERROR, _lib.load().gcb200_last_error().decode(errors="replace"))
 
     def destroy(self):
         if self._h:

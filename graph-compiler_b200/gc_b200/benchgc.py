@@ -208,6 +208,24 @@ def ref_run(fn: mlir_text.Func, tensors: Dict[str, torch.Tensor]) -> List[torch.
             env[op.out] = torch.max(x[0], torch.zeros_like(x[0]))
         elif op.name == "sigmoid":
             env[op.out] = torch.sigmoid(x[0])
+        elif op.name == "neg":
+            env[op.out] = torch.neg(x[0])
+        elif op.name == "exp":
+            env[op.out] = torch.exp(x[0])
+        elif op.name == "cast":
+            env[op.out] = x[0].to(compat.get_dtype(fn.values[op.out].type.dtype))
+        elif op.name == "reshape":
+            env[op.out] = x[0].reshape(fn.values[op.out].type.shape)
+        elif op.name == "pow":
+            env[op.out] = torch.pow(x[0], op.attrs["beta"])
+        elif op.name == "reduce_sum":
+            env[op.out] = torch.sum(x[0], dim=list(op.attrs["axes"]))
+        elif op.name == "softmax":
+            env[op.out] = torch.softmax(x[0], op.attrs["dimension"])
+        elif op.name == "batch_matmul":
+            a = x[0].transpose(-1, -2) if op.attrs["transpose_a"] else x[0]
+            b = x[1].transpose(-1, -2) if op.attrs["transpose_b"] else x[1]
+            env[op.out] = torch.matmul(a, b)
         else:
             raise mlir_text.Unimplemented(op.name)
     return [env[r] for r in fn.results]
@@ -221,7 +239,7 @@ def main(argv=None) -> int:
     try:
         text = _module_text(flags)
         fn = mlir_text.parse_module(text, flags.entry)
-        graph_json, arg_ids, out_ids = mlir_text.to_partition(fn)
+        graph_json, arg_ids, out_ids, consts = mlir_text.to_partition(fn)
     except mlir_text.Unimplemented as e:
         print(f"unimplemented: {e}", file=sys.stderr)
         return 3
@@ -258,6 +276,8 @@ def main(argv=None) -> int:
     compile_cost = (timeit.default_timer() - t0) * 1000
     used = set(json.loads(graph_json)["input_ports"])
     ins = {arg_ids[i]: tensors[v.name] for i, v in enumerate(fn.args) if arg_ids[i] in used}
+    # splat constants the module uses as operands travel as one-element inputs
+    ins.update({cid: torch.full((1,), val, dtype=compat.get_dtype(dt)) for cid, (val, dt) in consts.items() if cid in used})
     outs_b = dict(zip(out_ids, outs))
 
     if flags.mode == "C":

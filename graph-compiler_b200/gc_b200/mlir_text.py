@@ -4,7 +4,12 @@ benchgc hands the reference one `func.func` whose body is a straight line of
 `tensor.empty`, `arith.constant`, `linalg.fill`, `linalg.matmul[_transpose_a|_transpose_b]`,
 `linalg.broadcast`, `linalg.add|sub|mul|div`, `linalg.max` (against a zero splat: ReLU),
 `linalgx.sigmoid` and `return` (test/benchgc/src/benchgc/pattern/mlp.py:68-150,
-test/benchgc/src/benchgc/linalg/matmul.py).  No MLIR library is needed to read
+test/benchgc/src/benchgc/linalg/matmul.py); the reference's llama2 decoder case
+(test/benchgc/cases/llama2.mlir) adds `tensor.collapse_shape` / `tensor.expand_shape`,
+`linalg.copy` (a cast), `linalg.powf` by a splat, `linalg.reduce` with an add body,
+`linalg.negf`, `linalg.exp` and splat constants as operands; attention arrives as
+`linalg.batch_matmul_transpose_b` -> `linalg.mul` by a splat -> `linalg.softmax` ->
+`linalg.batch_matmul`, which is recognised as one fused partition.  No MLIR library is needed to read
 that subset: this module parses the text line by line into a list of ops over
 named SSA values, checks the shapes, and lowers the list to the oneDNN-graph
 JSON partition the C API compiles (the inverse of
@@ -138,6 +143,9 @@ def _clause(body: str, key: str) -> Optional[str]:
 
 
 _BINARY = {"linalg.add": "add", "linalg.sub": "sub", "linalg.mul": "mul", "linalg.div": "div"}
+_UNARY = {"linalgx.sigmoid": "sigmoid", "linalg.negf": "neg", "linalg.exp": "exp", "linalg.copy": "cast"}
+_BATCH_MATMUL = {"linalg.batch_matmul": (False, False), "linalg.batch_matmul_transpose_a": (True, False),
+                 "linalg.batch_matmul_transpose_b": (False, True)}
 _MATMUL = {"linalg.matmul": (False, False), "linalg.matmul_transpose_a": (True, False), "linalg.matmul_transpose_b": (False, True)}
 
 
@@ -147,6 +155,7 @@ def parse_module(text: str, entry: str = "entry") -> Func:
     fn = None
     body: List[str] = []
     depth_in = False
+    nest = 0   # regions opened inside the function body (linalg.reduce carries one)
     for ln in lines:
         s = ln.strip()
         if not depth_in:
@@ -155,8 +164,12 @@ def parse_module(text: str, entry: str = "entry") -> Func:
                 fn = m
                 depth_in = True
             continue
-        if s == "}":
+        if s == "}" and nest == 0:
             break
+        if s.endswith("{"):
+            nest += 1
+        elif s.startswith("}"):
+            nest -= 1
         if s:
             body.append(s)
     if fn is None:
@@ -183,7 +196,10 @@ def parse_module(text: str, entry: str = "entry") -> Func:
 
     ops: List[Op] = []
     results: List[str] = []
-    for s in body:
+    pos = 0
+    while pos < len(body):
+        s = body[pos]
+        pos += 1
         if s.startswith("return") or s.startswith("func.return"):
             rest = s.split("return", 1)[1].strip()
             if rest:
@@ -267,11 +283,90 @@ def parse_module(text: str, entry: str = "entry") -> Func:
             else:
                 ops.append(Op(_BINARY[opname], ins, res))
             values[res] = Value(res, ot[0], "op")
-        elif opname == "linalgx.sigmoid":
+        elif opname in _UNARY:
             ins, it = _operands(_clause(rhs, "ins"))
             outs, ot = _operands(_clause(rhs, "outs"))
             get(ins[0])
-            ops.append(Op("sigmoid", ins, res))
+            if it[0].shape != ot[0].shape:
+                raise ParseError(f"{opname}: operand shape differs from the result shape")
+            ops.append(Op(_UNARY[opname], ins, res))
+            values[res] = Value(res, ot[0], "op")
+        elif opname in ("tensor.collapse_shape", "tensor.expand_shape"):
+            m2 = re.match(r"tensor\.\w+\s+(%[\w#.]+)\s*\[(.*?)\]\s*(?:output_shape\s*\[[^\]]*\]\s*)?:\s*(tensor<.*?>)\s+into\s+(tensor<.*?>)\s*$", rhs)
+            if not m2:
+                raise ParseError(f"malformed reshape: {rhs!r}")
+            src, t_in, t_out = m2.group(1), parse_type(m2.group(3)), parse_type(m2.group(4))
+            if get(src).type.shape != t_in.shape:
+                raise ParseError(f"type of {src} does not match its definition")
+            n_in = n_out = 1
+            for d in t_in.shape:
+                n_in *= d
+            for d in t_out.shape:
+                n_out *= d
+            if n_in != n_out or t_in.dtype != t_out.dtype:
+                raise ParseError(f"{opname} changes the element count or type: {rhs!r}")
+            ops.append(Op("reshape", [src], res))
+            values[res] = Value(res, t_out, "op")
+        elif opname == "linalg.powf":
+            ins, it = _operands(_clause(rhs, "ins"))
+            outs, ot = _operands(_clause(rhs, "outs"))
+            e = get(ins[1])
+            if e.kind != "const":
+                raise Unimplemented("linalg.powf whose exponent is not a splat constant")
+            get(ins[0])
+            ops.append(Op("pow", [ins[0]], res, {"beta": e.const}))
+            values[res] = Value(res, ot[0], "op")
+        elif opname == "linalg.reduce":
+            ins, it = _operands(_clause(rhs, "ins"))
+            outs, ot = _operands(_clause(rhs, "outs"))
+            d = re.search(r"dimensions\s*=\s*\[([\d,\s]*)\]", rhs)
+            if not d:
+                raise ParseError("linalg.reduce without dimensions")
+            axes = [int(x) for x in d.group(1).split(",") if x.strip()]
+            # the combiner region follows on its own lines: only a sum (arith.addf of the two block arguments) is taken
+            region = []
+            while pos < len(body):
+                ln2 = body[pos]
+                pos += 1
+                region.append(ln2)
+                if ln2.startswith("}"):
+                    break
+            if not any("arith.addf" in r for r in region) or sum("arith." in r for r in region) != 1:
+                raise Unimplemented("linalg.reduce with a combiner other than addition")
+            init = get(outs[0])
+            if init.kind != "zero_fill":
+                raise Unimplemented("linalg.reduce whose init operand is not a zero fill")
+            kept = tuple(x for i, x in enumerate(it[0].shape) if i not in axes)
+            if kept != ot[0].shape:
+                raise ParseError(f"reduce of {it[0].shape} over {axes} does not give {ot[0].shape}")
+            get(ins[0])
+            ops.append(Op("reduce_sum", [ins[0]], res, {"axes": axes}))
+            values[res] = Value(res, ot[0], "op")
+        elif opname == "linalg.softmax":
+            d = re.search(r"dimension\((\d+)\)", rhs)
+            ins, it = _operands(_clause(rhs, "ins"))
+            outs, ot = _operands(_clause(rhs, "outs"))
+            if not d:
+                raise ParseError("linalg.softmax without dimension")
+            get(ins[0])
+            ops.append(Op("softmax", ins, res, {"dimension": int(d.group(1))}))
+            values[res] = Value(res, ot[0], "op")
+        elif opname in _BATCH_MATMUL:
+            ins, it = _operands(_clause(rhs, "ins"))
+            outs, ot = _operands(_clause(rhs, "outs"))
+            for n in ins:
+                get(n)
+            if get(outs[0]).kind != "zero_fill":
+                raise Unimplemented("linalg.batch_matmul whose init operand is not a zero fill")
+            ta, tb = _BATCH_MATMUL[opname]
+            a, b = it
+            if a.rank != 3 or b.rank != 3 or a.shape[0] != b.shape[0]:
+                raise ParseError("batch_matmul operands must be rank 3 with one batch size")
+            m_, k_ = (a.shape[2], a.shape[1]) if ta else a.shape[1:]
+            k2, n_ = (b.shape[2], b.shape[1]) if tb else b.shape[1:]
+            if k_ != k2 or ot[0].shape != (a.shape[0], m_, n_):
+                raise ParseError(f"batch_matmul shapes do not agree: {a.shape} x {b.shape} -> {ot[0].shape}")
+            ops.append(Op("batch_matmul", ins, res, {"transpose_a": ta, "transpose_b": tb}))
             values[res] = Value(res, ot[0], "op")
         else:
             raise Unimplemented(f"op {opname}")
@@ -285,51 +380,131 @@ def parse_module(text: str, entry: str = "entry") -> Func:
 
 
 # ------------------------------------------------------------------------------------- lowering
-_KIND = {"add": "Add", "sub": "Subtract", "mul": "Multiply", "div": "Divide", "relu": "ReLU", "sigmoid": "Sigmoid"}
+_KIND = {"add": "Add", "sub": "Subtract", "mul": "Multiply", "div": "Divide", "relu": "ReLU", "sigmoid": "Sigmoid",
+         "neg": "Negate", "exp": "Exp", "cast": "Typecast", "reshape": "StaticReshape", "pow": "Pow", "reduce_sum": "ReduceSum"}
 
 
-def to_partition(fn: Func) -> Tuple[str, List[int], List[int]]:
-    """The oneDNN-graph JSON of `fn`.  Returns (json text, input tensor ids in argument order, output ids).
+def _fuse_attention(fn: Func) -> List[Op]:
+    """batch_matmul_transpose_b(Q, K) [-> mul by a splat scale] -> softmax over the last dimension -> batch_matmul(., V),
+    every intermediate used once: one fused attention op (softmax as DecomposeAggregatedOps.cpp:24-38 defines it)."""
+    uses: Dict[str, int] = {}
+    for op in fn.ops:
+        for n in op.ins:
+            uses[n] = uses.get(n, 0) + 1
+    for r in fn.results:
+        uses[r] = uses.get(r, 0) + 1
+    by_out = {op.out: op for op in fn.ops}
+    out: List[Op] = []
+    dead = set()
+    for op in fn.ops:
+        if op.name != "batch_matmul" or op.attrs["transpose_a"] or op.attrs["transpose_b"]:
+            continue
+        sm = by_out.get(op.ins[0])
+        if not sm or sm.name != "softmax" or uses.get(sm.out, 0) != 1:
+            continue
+        if sm.attrs["dimension"] != fn.values[sm.out].type.rank - 1:
+            continue
+        scale, cur = 1.0, by_out.get(sm.ins[0])
+        if cur and cur.name == "mul" and uses.get(cur.out, 0) == 1:
+            consts = [n for n in cur.ins if fn.values[n].kind == "const"]
+            if len(consts) == 1:
+                scale = float(fn.values[consts[0]].const)
+                other = cur.ins[1] if cur.ins[0] == consts[0] else cur.ins[0]
+                dead.add(cur.out)
+                cur = by_out.get(other)
+        if not cur or cur.name != "batch_matmul" or cur.attrs["transpose_a"] or not cur.attrs["transpose_b"] or uses.get(cur.out, 0) != 1:
+            dead.discard(by_out[sm.ins[0]].out if sm.ins[0] in by_out else "")
+            continue
+        q, k, v = cur.ins[0], cur.ins[1], op.ins[1]
+        if not (fn.values[q].type.shape == fn.values[k].type.shape == fn.values[v].type.shape):
+            raise Unimplemented("attention with different Q, K and V shapes")
+        dead.update({cur.out, sm.out})
+        op.name, op.ins, op.attrs = "sdpa", [q, k, v], {"scale": scale}
+    for op in fn.ops:
+        if op.out not in dead:
+            out.append(op)
+    for op in out:
+        if op.name in ("softmax", "batch_matmul"):
+            raise Unimplemented(f"{op.name} outside the fused attention pattern")
+    return out
 
-    A broadcast along the leading dimensions becomes numpy auto-broadcast of its source
-    (lib/gc/Transforms/OneDNNGraphToLinalg.cpp:484-494 goes the other way).
+
+def to_partition(fn: Func):
+    """The oneDNN-graph JSON of `fn`.  Returns (json text, input tensor ids in argument order, output ids, constants),
+    where ``constants`` maps the id of every extra one-element input to its (value, dtype): splat constants that the
+    module uses as operands become partition inputs that the caller fills.
+
+    A broadcast becomes numpy auto-broadcast of its source, reshaped first when the new dimensions are not the
+    leading ones (lib/gc/Transforms/OneDNNGraphToLinalg.cpp:484-494 goes the other way).
     """
     ids: Dict[str, int] = {a.name: i for i, a in enumerate(fn.args)}
     nxt = len(fn.args)
+    consts: Dict[int, Tuple[float, str]] = {}
+    const_ids: Dict[Tuple[float, str], int] = {}
+    graph: List[dict] = []
+    reshaped: Dict[Tuple[str, Tuple[int, ...]], dict] = {}
+
+    def fresh() -> int:
+        nonlocal nxt
+        nxt += 1
+        return nxt - 1
+
+    def node(kind: str, ins: List[dict], outs: List[dict], attrs: Optional[dict] = None):
+        graph.append({"id": len(graph), "name": f"{kind.lower()}_{len(graph)}", "kind": kind, "attrs": attrs or {}, "inputs": ins,
+                      "outputs": outs})
 
     def tensor(name: str) -> dict:
         v = fn.values[name]
         if v.kind == "bcast":
+            src = tensor(v.src)
             lead = tuple(range(len(v.bdims)))
-            if v.bdims != lead:
-                raise Unimplemented("broadcast along a non-leading dimension")
-            return tensor(v.src)
-        if v.kind in ("const", "zero_fill", "empty"):
-            raise Unimplemented(f"{name}: a constant or uninitialised tensor as a graph input")
+            if v.bdims == lead:
+                return src
+            # new dimensions in the middle or at the end: give the source size-1 dimensions there, then auto-broadcast
+            shape = tuple(1 if i in v.bdims else d for i, d in enumerate(v.type.shape))
+            key = (v.src, shape)
+            if key not in reshaped:
+                out = {"id": fresh(), "dtype": src["dtype"], "shape": list(shape)}
+                node("StaticReshape", [src], [out])
+                reshaped[key] = out
+            return reshaped[key]
+        if v.kind == "const" or v.kind == "zero_fill":
+            key = (float(v.const or 0.0), v.type.dtype)
+            if key not in const_ids:
+                const_ids[key] = fresh()
+                consts[const_ids[key]] = key
+            return {"id": const_ids[key], "dtype": v.type.dtype, "shape": [1], "property_type": "constant"}
+        if v.kind == "empty":
+            raise Unimplemented(f"{name}: an uninitialised tensor as an operand")
         if name not in ids:
             raise ParseError(f"{name} is used before it is produced")
         return {"id": ids[name], "dtype": v.type.dtype, "shape": list(v.type.shape)}
 
-    graph = []
-    for k, op in enumerate(fn.ops):
+    for op in _fuse_attention(fn):
         ins = [tensor(n) for n in op.ins]
-        ids[op.out] = nxt
-        nxt += 1
-        node = {"id": k, "name": f"{op.name}_{k}", "kind": "MatMul" if op.name == "matmul" else _KIND[op.name], "attrs": {},
-                "inputs": ins, "outputs": [tensor(op.out)]}
+        ids[op.out] = fresh()
+        out = tensor(op.out)
         if op.name == "matmul":
-            for a in ("transpose_a", "transpose_b"):
-                if op.attrs[a]:
-                    node["attrs"][a] = {"type": "bool", "value": 1}
+            attrs = {a: {"type": "bool", "value": 1} for a in ("transpose_a", "transpose_b") if op.attrs[a]}
+            node("MatMul", ins, [out], attrs)
+        elif op.name == "sdpa":
+            node("SDPA", ins, [out], {"scale": {"type": "f32", "value": op.attrs["scale"]}, "causal": {"type": "bool", "value": 0}})
         elif op.name in ("add", "sub", "mul", "div"):
-            node["attrs"]["auto_broadcast"] = {"type": "string", "value": "numpy"}
-        graph.append(node)
+            node(_KIND[op.name], ins, [out], {"auto_broadcast": {"type": "string", "value": "numpy"}})
+        elif op.name == "pow":
+            node("Pow", ins, [out], {"beta": {"type": "f32", "value": float(op.attrs["beta"])}})
+        elif op.name == "reduce_sum":
+            node("ReduceSum", ins, [out], {"axes": {"type": "s64[]", "value": list(op.attrs["axes"])}, "keep_dims": {"type": "bool", "value": 0}})
+        elif op.name in _KIND:
+            node(_KIND[op.name], ins, [out])
+        else:
+            raise Unimplemented(op.name)
     used = {t["id"] for n in graph for t in n["inputs"]}
-    in_ids = [ids[a.name] for a in fn.args if ids[a.name] in used]
+    in_ids = [ids[a.name] for a in fn.args if ids[a.name] in used] + [c for c in consts if c in used]
     out_ids = [ids[r] for r in fn.results]
     js = {"version": "3.5.0", "engine_kind": "cpu", "fpmath_mode": "strict", "input_ports": in_ids, "output_ports": out_ids,
           "graph": graph}
-    return json.dumps(js), [ids[a.name] for a in fn.args], out_ids
+    return json.dumps(js), [ids[a.name] for a in fn.args], out_ids, consts
 
 
 # ------------------------------------------------------------------------------------- printers
@@ -416,3 +591,109 @@ def matmul_module(case: str, a: TensorType, b: TensorType, c: TensorType, entry:
         f"    %1 = linalg.fill ins(%cst : {et}) outs(%0 : {tc}) -> {tc}",
         f"    %2 = linalg.{case} {{cast = #linalg.type_fn<cast_signed>}} ins(%arg0, %arg1 : {ta}, {tb}) outs(%1 : {tc}) -> {tc}",
         f"    return %2 : {tc}", "  }", "}"]) + "\n"
+
+
+def llama2_mlp_module(batch: int = 1, seq: int = 32, hidden: int = 4096, inter: int = 11008, entry: str = "entry") -> str:
+    """Text of a llama2 decoder block's second half in linalg form, the module the reference keeps as its
+    ``--driver mlir`` case (test/benchgc/cases/llama2.mlir): attention output projection + residual, RMSNorm,
+    gate / up projections with SiLU spelled as negf, exp, add 1, div, the down projection + residual, RMSNorm.
+    Arguments: x [B,S,H], w_o [H,H], residual [B,S,H], eps1 [1] f32 (unused), g1 [H], w_gate [I,H], w_up [I,H],
+    w_down [H,I], eps2 [1] f32, g2 [H]; results: the normalised output and the second residual sum."""
+    B, S, H, I, T = batch, seq, hidden, inter, batch * seq
+    bf = lambda *d: _ty(d, "bf16")
+    f = lambda *d: _ty(d, "f32")
+    L: List[str] = []
+    n = 0
+
+    def emit(rhs: str, name: Optional[str] = None) -> str:
+        nonlocal n
+        if name is None:
+            name = f"%{n}"
+            n += 1
+        L.append(f"    {name} = {rhs}")
+        return name
+
+    def empty(t: str) -> str:
+        return emit(f"tensor.empty() : {t}")
+
+    def zero(t: str, et: str) -> str:
+        c = emit(f"arith.constant 0.000000e+00 : {et}", f"%z{len(L)}")
+        return emit(f"linalg.fill ins({c} : {et}) outs({empty(t)} : {t}) -> {t}")
+
+    def binary(op: str, a: str, b: str, t: str) -> str:
+        return emit(f"linalg.{op} ins({a}, {b} : {t}, {t}) outs({empty(t)} : {t}) -> {t}")
+
+    def splat(v: float, t: str) -> str:
+        return emit(f"arith.constant dense<{v:e}> : {t}", f"%c{len(L)}")
+
+    def proj(x2: str, w: str, rows: int, k: int, nn: int) -> str:
+        return emit(f"linalg.matmul_transpose_b ins({x2}, {w} : {bf(rows, k)}, {bf(nn, k)}) outs({zero(bf(rows, nn), 'bf16')} : "
+                    f"{bf(rows, nn)}) -> {bf(rows, nn)}")
+
+    def rmsnorm(x: str, eps: str, gamma: str) -> str:
+        xf = emit(f"linalg.copy ins({x} : {bf(B, S, H)}) outs({empty(f(B, S, H))} : {f(B, S, H)}) -> {f(B, S, H)}")
+        sq = emit(f"linalg.powf ins({xf}, {splat(2.0, f(B, S, H))} : {f(B, S, H)}, {f(B, S, H)}) outs({empty(f(B, S, H))} : {f(B, S, H)}) -> {f(B, S, H)}")
+        init = zero(f(B, S), "f32")
+        red = emit(f"linalg.reduce ins({sq} : {f(B, S, H)}) outs({init} : {f(B, S)}) dimensions = [2]", f"%reduced{len(L)}")
+        L.extend(["      (%in: f32, %init: f32) {", "        %sum = arith.addf %in, %init : f32", "        linalg.yield %sum : f32", "      }"])
+        mean = binary("div", red, splat(float(H), f(B, S)), f(B, S))
+        m3 = emit(f"tensor.expand_shape {mean} [[0], [1, 2]] output_shape [{B}, {S}, 1] : {f(B, S)} into {f(B, S, 1)}", f"%expanded{len(L)}")
+        eb = emit(f"linalg.broadcast ins({eps} : {f(1)}) outs({empty(f(B, S, 1))} : {f(B, S, 1)}) dimensions = [0, 1]", f"%broadcasted{len(L)}")
+        ve = binary("add", m3, eb, f(B, S, 1))
+        rs = emit(f"linalg.powf ins({ve}, {splat(-0.5, f(B, S, 1))} : {f(B, S, 1)}, {f(B, S, 1)}) outs({empty(f(B, S, 1))} : {f(B, S, 1)}) -> {f(B, S, 1)}")
+        r2 = emit(f"tensor.collapse_shape {rs} [[0], [1, 2]] : {f(B, S, 1)} into {f(B, S)}", f"%collapsed{len(L)}")
+        rb = emit(f"linalg.broadcast ins({r2} : {f(B, S)}) outs({empty(f(B, S, H))} : {f(B, S, H)}) dimensions = [2]", f"%broadcasted{len(L)}")
+        y = binary("mul", xf, rb, f(B, S, H))
+        yb = emit(f"linalg.copy ins({y} : {f(B, S, H)}) outs({empty(bf(B, S, H))} : {bf(B, S, H)}) -> {bf(B, S, H)}")
+        gb = emit(f"linalg.broadcast ins({gamma} : {bf(H)}) outs({empty(bf(B, S, H))} : {bf(B, S, H)}) dimensions = [0, 1]", f"%broadcasted{len(L)}")
+        return binary("mul", gb, yb, bf(B, S, H))
+
+    sig = (f"%arg0: {bf(B, S, H)}, %arg1: {bf(H, H)}, %arg2: {bf(B, S, H)}, %arg3: {f(1)}, %arg4: {bf(H)}, %arg5: {bf(I, H)}, "
+           f"%arg6: {bf(I, H)}, %arg7: {bf(H, I)}, %arg8: {f(1)}, %arg9: {bf(H)}")
+    head = ["module {", f"  func.func @{entry}({sig}) -> ({bf(B, S, H)}, {bf(B, S, H)}) attributes {{llvm.emit_c_interface}} {{"]
+    x2 = emit(f"tensor.collapse_shape %arg0 [[0, 1], [2]] : {bf(B, S, H)} into {bf(T, H)}", "%collapsed")
+    o = proj(x2, "%arg1", T, H, H)
+    o3 = emit(f"tensor.expand_shape {o} [[0, 1], [2]] output_shape [{B}, {S}, {H}] : {bf(T, H)} into {bf(B, S, H)}", "%expanded")
+    r1 = binary("add", "%arg2", o3, bf(B, S, H))
+    h = rmsnorm(r1, "%arg8", "%arg4")
+    h2 = emit(f"tensor.collapse_shape {h} [[0, 1], [2]] : {bf(B, S, H)} into {bf(T, H)}", f"%collapsed{len(L)}")
+    gate = proj(h2, "%arg5", T, H, I)
+    g3 = emit(f"tensor.expand_shape {gate} [[0, 1], [2]] output_shape [{B}, {S}, {I}] : {bf(T, I)} into {bf(B, S, I)}", f"%expanded{len(L)}")
+    one = splat(1.0, bf(B, S, I))
+    ng = emit(f"linalg.negf ins({g3} : {bf(B, S, I)}) outs({empty(bf(B, S, I))} : {bf(B, S, I)}) -> {bf(B, S, I)}")
+    ex = emit(f"linalg.exp ins({ng} : {bf(B, S, I)}) outs({empty(bf(B, S, I))} : {bf(B, S, I)}) -> {bf(B, S, I)}")
+    den = binary("add", one, ex, bf(B, S, I))
+    sg = binary("div", one, den, bf(B, S, I))
+    silu = binary("mul", sg, g3, bf(B, S, I))
+    h2b = emit(f"tensor.collapse_shape {h} [[0, 1], [2]] : {bf(B, S, H)} into {bf(T, H)}", f"%collapsed{len(L)}")
+    up = proj(h2b, "%arg6", T, H, I)
+    u3 = emit(f"tensor.expand_shape {up} [[0, 1], [2]] output_shape [{B}, {S}, {I}] : {bf(T, I)} into {bf(B, S, I)}", f"%expanded{len(L)}")
+    act = binary("mul", silu, u3, bf(B, S, I))
+    a2 = emit(f"tensor.collapse_shape {act} [[0, 1], [2]] : {bf(B, S, I)} into {bf(T, I)}", f"%collapsed{len(L)}")
+    down = proj(a2, "%arg7", T, I, H)
+    d3 = emit(f"tensor.expand_shape {down} [[0, 1], [2]] output_shape [{B}, {S}, {H}] : {bf(T, H)} into {bf(B, S, H)}", f"%expanded{len(L)}")
+    r2 = binary("add", r1, d3, bf(B, S, H))
+    out = rmsnorm(r2, "%arg8", "%arg9")
+    return "\n".join(head + L + [f"    return {out}, {r2} : {bf(B, S, H)}, {bf(B, S, H)}", "  }", "}"]) + "\n"
+
+
+def attention_module(batch_heads: int, seq: int, dim: int, scale: float, entry: str = "entry") -> str:
+    """Attention spelled with the ops the reference's drivers emit one by one (linalg/matmul.py batch_matmul*,
+    linalg/softmax.py): scores = Q K^T, scaled, softmax over the keys, times V."""
+    t, ts = _ty((batch_heads, seq, dim), "bf16"), _ty((batch_heads, seq, seq), "bf16")
+    return "\n".join([
+        "module {",
+        f"  func.func @{entry}(%arg0: {t}, %arg1: {t}, %arg2: {t}) -> {t} attributes {{llvm.emit_c_interface}} {{",
+        "    %cst = arith.constant 0.000000e+00 : bf16",
+        f"    %0 = tensor.empty() : {ts}",
+        f"    %1 = linalg.fill ins(%cst : bf16) outs(%0 : {ts}) -> {ts}",
+        f"    %2 = linalg.batch_matmul_transpose_b ins(%arg0, %arg1 : {t}, {t}) outs(%1 : {ts}) -> {ts}",
+        f"    %cst_0 = arith.constant dense<{scale:e}> : {ts}",
+        f"    %3 = tensor.empty() : {ts}",
+        f"    %4 = linalg.mul ins(%2, %cst_0 : {ts}, {ts}) outs(%3 : {ts}) -> {ts}",
+        f"    %5 = tensor.empty() : {ts}",
+        f"    %6 = linalg.softmax dimension(2) ins(%4 : {ts}) outs(%5 : {ts}) -> {ts}",
+        f"    %7 = tensor.empty() : {t}",
+        f"    %8 = linalg.fill ins(%cst : bf16) outs(%7 : {t}) -> {t}",
+        f"    %9 = linalg.batch_matmul ins(%6, %arg2 : {ts}, {t}) outs(%8 : {t}) -> {t}",
+        f"    return %9 : {t}", "  }", "}"]) + "\n"

@@ -212,6 +212,22 @@ int gcb200_execute_on_stream(const struct dnnl_graph_compiler_executable *exe, s
 int gcb200_plan_dump(const struct dnnl_graph_compiler_executable *exe, char *buf, size_t cap, size_t *needed);
 int gcb200_plan_arena(const int64_t *bytes, const int *first, const int *last, int n, int64_t align, int64_t *offsets,
                       int64_t *total);
+/* Observability, in the reference's terms.  GC_DEBUG=<extended regex over source file paths> enables the
+ * "[DEBUG] [file:line] ..." lines of the matching files on stdout, errors always go to stderr as "[ERROR] ..."
+ * (include/gc/Utils/Log.h:43-66).  GC_B200_VERBOSE=1 prints, per compiled partition, what
+ * gcb200_describe_launches returns: one line per step with the kernel and, for matmuls, tile, K split, pipeline
+ * depth and grid as chosen for `sm_count` SMs (the reference prints its choice under LLVM_DEBUG,
+ * lib/gc/Analysis/MatmulConfigAnalysis.cpp:544-546).  Needs no device. */
+int gcb200_describe_launches(const struct dnnl_graph_compiler_executable *exe, int sm_count, char *buf, size_t cap, size_t *needed);
+/* Debug guard bands.  With GC_B200_GUARD=<bytes> in the environment when a partition is COMPILED, every slice of its
+ * workspace arena is planned with that many bytes (rounded up to 256) of canary before and after it; every
+ * synchronous execute then checks the bands and fails with dnnl_runtime_error naming the tensor whose band was
+ * overwritten (the reference's debug memory pool keeps such a canary per allocation,
+ * lib/gc/ExecutionEngine/CPURuntime/MemoryPool.cpp:55-60, :213-217).  gcb200_guard_check runs the check on demand
+ * (synchronises the device); gcb200_guard_selftest damages one band from the host, the way a stray store would,
+ * so that the detection itself can be tested without any out-of-bounds access on the GPU. */
+int gcb200_guard_check(const struct dnnl_graph_compiler_executable *exe, int *damaged_bands);
+int gcb200_guard_selftest(const struct dnnl_graph_compiler_executable *exe);
 /* The planner on a raw trace, with the reference's interface (memoryplan::scheduleMemoryAllocations,
  * include/gc/Transforms/StaticMemoryPlanning.h:57-62): trace i allocates trace_size[i] elements for buffer
  * trace_buffer[i], or releases it when the size is 0; hint i says buffer hint_buffer[i] may take over

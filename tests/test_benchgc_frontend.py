@@ -14,7 +14,8 @@ def test_mlp_module_text_round_trips_to_the_partition_the_c_api_takes():
     fn = mlir_text.parse_module(text)
     assert [a.type.shape for a in fn.args] == [(128, 512), (512, 256), (256,)]
     assert [o.name for o in fn.ops] == ["matmul", "add", "relu"]
-    js, arg_ids, out_ids = mlir_text.to_partition(fn)
+    js, arg_ids, out_ids, consts = mlir_text.to_partition(fn)
+    assert consts == {}
     g = json.loads(js)
     assert [n["kind"] for n in g["graph"]] == ["MatMul", "Add", "ReLU"]
     assert g["input_ports"] == [0, 1, 2] and arg_ids == [0, 1, 2] and g["output_ports"] == out_ids
@@ -56,7 +57,7 @@ def test_single_op_modules_and_transposes():
 
 
 @pytest.mark.parametrize("stmt, err", [
-    ("%9 = linalg.exp ins(%arg0 : tensor<4x4xf32>) outs(%0 : tensor<4x4xf32>) -> tensor<4x4xf32>", mlir_text.Unimplemented),
+    ("%9 = linalg.tanh ins(%arg0 : tensor<4x4xf32>) outs(%0 : tensor<4x4xf32>) -> tensor<4x4xf32>", mlir_text.Unimplemented),
     ("%9 = tensor.empty() : tensor<?x4xf32>", mlir_text.Unimplemented),
     ("%9 = linalg.add ins(%arg0, %nope : tensor<4x4xf32>, tensor<4x4xf32>) outs(%0 : tensor<4x4xf32>) -> tensor<4x4xf32>", mlir_text.ParseError),
 ])
@@ -100,3 +101,83 @@ def test_default_fills_and_thresholds_follow_the_harness():
         x.dtype, x.shape = "bf16", [4, 4]
     benchgc._defaults(pf, pa, 1)
     assert (pa[0].fill_type, pa[0].fill_param) == ("U", ["0", "1"]) and pa[1].cmp_param == ["0.05", "100.0"]
+
+
+def _llama2_reference(t, H):
+    """The block in torch, op by op in each tensor's own dtype (what benchgc's evaluators compute)."""
+    x, wo, res, _, g1, wg, wu, wd, eps, g2 = (t[f"%arg{i}"] for i in range(10))
+
+    def rms(v, gamma):
+        f = v.float()
+        r = (torch.sum(torch.pow(f, 2.0), dim=[2]) / torch.full((1,), float(H))).reshape(f.shape[0], f.shape[1], 1)
+        r = torch.pow(r + eps.reshape(1, 1, 1), -0.5)
+        return gamma * (f * r).to(torch.bfloat16)
+
+    r1 = res + torch.matmul(x.reshape(-1, H), wo.t()).reshape(x.shape)
+    h = rms(r1, g1)
+    gate = torch.matmul(h.reshape(-1, H), wg.t()).reshape(x.shape[0], x.shape[1], -1)
+    one = torch.ones_like(gate)
+    silu = (one / (one + torch.exp(torch.neg(gate)))) * gate
+    up = torch.matmul(h.reshape(-1, H), wu.t()).reshape(gate.shape)
+    r2 = r1 + torch.matmul((silu * up).reshape(-1, gate.shape[-1]), wd.t()).reshape(x.shape)
+    return rms(r2, g2), r2
+
+
+def test_llama2_decoder_block_in_linalg_form_lowers_to_a_partition():
+    """The reference's own --driver mlir case (test/benchgc/cases/llama2.mlir) in small: collapse / expand_shape, copy as
+    cast, powf by a splat, reduce with an add body, broadcasts along trailing dimensions, splat constants as operands."""
+    B, S, H, I = 1, 8, 64, 96
+    text = mlir_text.llama2_mlp_module(B, S, H, I)
+    fn = mlir_text.parse_module(text)
+    names = [o.name for o in fn.ops]
+    assert names.count("matmul") == 4 and names.count("reshape") == 12 and names.count("reduce_sum") == 2 and names.count("pow") == 4
+    assert names.count("cast") == 4 and names.count("neg") == 1 and names.count("exp") == 1
+    js, arg_ids, out_ids, consts = mlir_text.to_partition(fn)
+    g = json.loads(js)
+    kinds = [n["kind"] for n in g["graph"]]
+    for k in ("MatMul", "StaticReshape", "Typecast", "Pow", "ReduceSum", "Negate", "Exp", "Divide", "Multiply", "Add"):
+        assert k in kinds, k
+    assert sorted(v for v in consts.values()) == [(1.0, "bf16"), (float(H), "f32")]   # the splats used as operands
+    assert 3 not in g["input_ports"]                       # %arg3 (an unused epsilon) is not a partition input
+    assert len(out_ids) == 2
+    # the host interpretation of the parsed module equals the block written directly in torch
+    torch.manual_seed(0)
+    t = {a.name: (torch.randn(a.type.shape) * (0.1 if a.type.rank == 2 else 1.0)).to(benchgc.compat.get_dtype(a.type.dtype)) for a in fn.args}
+    t["%arg8"] = torch.full((1,), 1e-5)
+    got = benchgc.ref_run(fn, t)
+    want = _llama2_reference(t, H)
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    # the partition compiles (host only)
+    from gc_b200 import api
+    plan = api.GraphCompiler().compile(js).plan()
+    assert plan.count("step") >= 30
+
+
+def test_the_reference_llama2_case_file_parses_when_the_checkout_is_present():
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.environ.get("GC_REFERENCE_DIR") or os.path.join(os.path.dirname(root), "reference")
+    path = os.path.join(ref, "test", "benchgc", "cases", "llama2.mlir")
+    if not os.path.exists(path):
+        pytest.skip("reference checkout not present")
+    fn = mlir_text.parse_module(open(path).read())
+    mine = mlir_text.parse_module(mlir_text.llama2_mlp_module(1, 32, 4096, 11008))
+    assert [o.name for o in fn.ops] == [o.name for o in mine.ops]                      # same op sequence as the generator's
+    assert [a.type.shape for a in fn.args] == [a.type.shape for a in mine.args]
+    js, _, out_ids, consts = mlir_text.to_partition(fn)
+    assert len(out_ids) == 2 and len(consts) == 2
+
+
+def test_attention_in_linalg_form_becomes_one_fused_partition():
+    text = mlir_text.attention_module(4, 256, 128, 0.125)
+    fn = mlir_text.parse_module(text)
+    assert [o.name for o in fn.ops] == ["batch_matmul", "mul", "softmax", "batch_matmul"]
+    js, arg_ids, out_ids, consts = mlir_text.to_partition(fn)
+    g = json.loads(js)
+    assert [n["kind"] for n in g["graph"]] == ["SDPA"] and consts == {}
+    assert g["graph"][0]["attrs"]["scale"]["value"] == 0.125 and g["input_ports"] == [0, 1, 2]
+    # a softmax that is not part of the pattern is refused
+    lone = text.replace("linalg.batch_matmul ins(%6, %arg2", "linalg.batch_matmul ins(%4, %arg2")
+    with pytest.raises(mlir_text.Unimplemented):
+        mlir_text.to_partition(mlir_text.parse_module(lone))

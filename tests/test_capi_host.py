@@ -130,6 +130,54 @@ def test_column_sum_scratch_is_not_shared_with_other_temporaries():
     assert M * N * 4 not in offs and set(offs) == {0, M * N * 4 + 1024, 2 * M * N * 4 + 1024}, plan
 
 
+def test_debug_log_filter_and_verbose_plan_follow_the_reference_switches():
+    """GC_DEBUG is an extended regex over source paths (include/gc/Utils/Log.h:43-66): matching files print
+    "[DEBUG] [file:line] ..." lines on stdout; GC_B200_VERBOSE prints the launch plan with the chosen tiles at compile.
+    Both are read once per process, so each setting runs in a child process."""
+    import subprocess
+    import sys
+
+    prog = ("import sys; sys.path[:0] = [%r, %r]\n"
+            "from gc_b200 import api, partitions\n"
+            "exe = api.GraphCompiler().compile(partitions.mlp(512, (4096, 16384, 4096))[0])\n"
+            "print('LAUNCHES', exe.launches().count('gemm_kernel'))\n") % (ROOT, os.path.join(ROOT, "graph-compiler_b200"))
+
+    def run(**env):
+        e = dict(os.environ)
+        for k in ("GC_DEBUG", "GC_B200_VERBOSE"):
+            e.pop(k, None)
+        e.update(env)
+        r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=e, timeout=120)
+        assert r.returncode == 0, r.stderr
+        return r.stdout
+
+    quiet = run()
+    assert "[DEBUG]" not in quiet and "launch plan" not in quiet and "LAUNCHES 2" in quiet
+    dbg = run(GC_DEBUG=".*")
+    assert re.search(r"\[DEBUG\] \[.*executable\.cu:\d+\] compiled a partition of 4 ops into 2 steps", dbg), dbg
+    assert "[DEBUG]" in run(GC_DEBUG="execut(able|or)") and "[DEBUG]" not in run(GC_DEBUG="/NoSuchDir/")
+    verbose = run(GC_B200_VERBOSE="1")
+    assert "[gc_b200] launch plan" in verbose
+    assert re.search(r"step 0 MatMul\+ReLU: gemm_kernel<bf16> 512x16384x4096 tile 128x\d+ splits 1 stages \d+ K blocks/stage \d+ grid 148", verbose), verbose
+    assert re.search(r"step 1 MatMul\+ReLU: gemm_kernel<bf16> 512x4096x16384 tile 128x\d+ splits 2 .* \+ reduce_planes", verbose), verbose
+
+
+def test_guard_bands_are_planned_around_every_arena_slice(monkeypatch):
+    """GC_B200_GUARD=<bytes> at compile time: each temporary gets a canary band before and after it (the debug
+    memory pool of the reference keeps one per allocation, MemoryPool.cpp:55-60); offsets move, sizes grow, the
+    slices still never overlap."""
+    js = partitions.mlp(128, (512, 64, 256), has_bias=[True, True])[0]
+    plain = api.GraphCompiler().compile(js).plan()
+    assert "guard_bytes" not in plain and "arena_bytes: 16384" in plain and "@arena+0" in plain
+    monkeypatch.setenv("GC_B200_GUARD", "100")                      # rounded up to 256
+    guarded = api.GraphCompiler().compile(js).plan()
+    assert "guard_bytes: 256 (2 bands)" in guarded
+    assert "arena_bytes: %d" % (16384 + 2 * 256 + 512) in guarded   # slice sizes are 1 KiB aligned: 16896 -> 17408
+    assert "@arena+256" in guarded
+    monkeypatch.delenv("GC_B200_GUARD")
+    assert api.GraphCompiler().compile(js).plan() == plain
+
+
 def test_mpl_graph_structure():
     """The 2-layer MLP of test/dnnl/resources/mpl.json (TestJsonParser.cpp:138-225): arguments
     0,1,2,5,7 in first-use order, result 9; both spellings of bias (+ReLU) fuse into the matmuls."""
