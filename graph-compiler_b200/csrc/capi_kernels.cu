@@ -109,7 +109,7 @@ GCB_EXPORT int gcb200_matmul_bf16_cfg(const void *A, const void *B, const void *
     require(cfg != nullptr, "cfg is null");
     require(cfg->bn >= 16 && cfg->bn <= 256 && cfg->bn % 16 == 0, "bn must be a multiple of 16 in [16,256]");
     require(cfg->swapped || cfg->bn >= 64, "row-major tiles need bn >= 64");
-    require(!cfg->pair || (!cfg->swapped && cfg->bn % 128 == 0), "the CTA-pair kernel needs bn in {128, 256} and the row-major orientation");
+    require(!cfg->pair || (!cfg->swapped && cfg->bn % 32 == 0), "the CTA-pair kernel needs bn a multiple of 32 (each CTA stages half the columns) and the row-major orientation");
     require(cfg->stages >= 2 && cfg->stages <= 8, "stages must be in [2,8]");
     require(cfg->splits >= 1 && cfg->group_m >= 1, "splits and group_m must be positive");
     MatmulConfig c{cfg->swapped, cfg->bn, cfg->splits, cfg->stages, cfg->group_m, cfg->grid, cfg->pair, cfg->kpb};

@@ -121,6 +121,12 @@ __global__ void unary_kernel(EwParams p, const void *a, void *o) {
   }
 }
 
+// acc[m, n] -= comp[n]: the zero-point term of a u8 x s8 product whose accumulators are the result themselves
+__global__ void sub_comp_kernel(int32_t *acc, const int32_t *comp, long long total, int N) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    acc[i] -= comp[int(i % N)];
+}
+
 struct ReduceParams {
   int rank;
   long long out_total, red_total;
@@ -430,6 +436,14 @@ struct dnnl_graph_compiler_executable {
                bool own_stream, bool sync) const {
     std::lock_guard<std::mutex> g(mu);
     prepare();
+    {
+      // streams, arena and staging buffers belong to the device that was current at the first call
+      int cur = -1;
+      GCB_CUDA(cudaGetDevice(&cur));
+      if (cur != device)
+        throw std::runtime_error("this executable is bound to CUDA device " + std::to_string(device) + " (current at its first execute); the current device is " +
+                                 std::to_string(cur));
+    }
     cudaStream_t s = own_stream ? stream : user_stream;
     const Partition &p = plan.part;
     const size_t ni = p.input_ids.size(), no = p.output_ids.size();
@@ -686,6 +700,21 @@ struct dnnl_graph_compiler_executable {
       }
       MatmulArgs m;
       m.A = addr(st.in[0]); m.B = addr(st.in[1]); m.M = st.M; m.N = st.N; m.K = st.K; m.int8 = 1;
+      if (st.raw_acc) {
+        // accumulators only: the raw s32 sums, then the zero-point term taken off per column
+        m.out_kind = OUT_S32; m.out = addr(st.out[0]);
+        if (!(tma_compatible(m.A, st.K, 1) && tma_compatible(m.B, st.N, 1)))
+          throw std::logic_error("QuantizedMatMul needs K and N to be multiples of 16");
+        m.scratch = splitk.ptr; m.scratch_bytes = splitk.bytes;
+        matmul_tc(m, s);
+        if (st.zp_a != 0) {
+          const long long total = (long long)st.M * st.N;
+          sub_comp_kernel<<<int(std::min<long long>((total + 255) / 256, 148LL * 16)), 256, 0, s>>>(static_cast<int32_t *>(addr(st.out[0])), comp, total, int(st.N));
+          GCB_CUDA(cudaGetLastError());
+          count_launch();
+        }
+        break;
+      }
       m.out_kind = OUT_DEQUANT_F32; m.out = addr(st.out[0]);
       m.scale = static_cast<const float *>(addr(st.in[2]));
       m.comp = comp;

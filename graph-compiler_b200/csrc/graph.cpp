@@ -374,17 +374,23 @@ Plan build_plan(Partition part) {
     } else if (op.kind == "QuantizedMatMul") {
       // extension: inputs src u8 [M,K], weights s8 [K,N], scales f32 [N], optional bias f32 [N];
       // outputs dst f32 [M,N] and optionally the raw s32 accumulators [M,N]; attr src_zp (s64)
-      if (op.inputs.size() < 3 || op.inputs.size() > 4 || op.outputs.empty() || op.outputs.size() > 2) invalid("QuantizedMatMul expects 3 or 4 inputs and 1 or 2 outputs");
-      if (op.inputs[0].dtype != DType::U8 || op.inputs[1].dtype != DType::S8 || op.inputs[2].dtype != DType::F32 ||
-          op.outputs[0].dtype != DType::F32)
-        unsupported("QuantizedMatMul supports u8 x s8 -> f32 with f32 scales");
+      // a third form: src and weights only, one s32 output - the zero-point-corrected accumulators
+      // sum_k (src[m,k] - src_zp) * w[k,n] without dequantisation (what linalg.quantized_matmul computes)
+      const bool raw = op.inputs.size() == 2 && op.outputs.size() == 1 && op.outputs[0].dtype == DType::S32;
+      if (!raw && (op.inputs.size() < 3 || op.inputs.size() > 4 || op.outputs.empty() || op.outputs.size() > 2))
+        invalid("QuantizedMatMul expects 3 or 4 inputs and 1 or 2 outputs (or 2 inputs and one s32 output)");
+      if (op.inputs[0].dtype != DType::U8 || op.inputs[1].dtype != DType::S8 ||
+          (!raw && (op.inputs[2].dtype != DType::F32 || op.outputs[0].dtype != DType::F32)))
+        unsupported("QuantizedMatMul supports u8 x s8 -> f32 with f32 scales, or -> s32");
       if (op.inputs[0].shape.size() != 2 || op.inputs[1].shape.size() != 2) invalid("QuantizedMatMul operands must be 2-D");
       st.kind = StepKind::QMATMUL;
       st.M = op.inputs[0].shape[0];
       st.K = op.inputs[0].shape[1];
       st.N = op.inputs[1].shape[1];
+      st.raw_acc = raw;
       if (op.inputs[1].shape[0] != st.K) invalid("QuantizedMatMul inner dimensions do not match");
-      if (op.inputs[2].numel() != st.N) invalid("QuantizedMatMul needs one scale per output channel");
+      if (op.outputs[0].numel() != st.M * st.N) invalid("QuantizedMatMul output shape does not match");
+      if (!raw && op.inputs[2].numel() != st.N) invalid("QuantizedMatMul needs one scale per output channel");
       st.has_bias = op.inputs.size() == 4;
       if (st.has_bias && (op.inputs[3].dtype != DType::F32 || op.inputs[3].numel() != st.N)) invalid("QuantizedMatMul bias must be f32 [N]");
       if (op.outputs.size() == 2 && op.outputs[1].dtype != DType::S32) invalid("second output must be s32");

@@ -79,6 +79,7 @@ struct Step {
   bool has_bias = false;          // bias is in[2]
   int64_t zp_a = 0;               // QMATMUL
   int scratch_slot = -1;          // QMATMUL: arena temp for column sums
+  bool raw_acc = false;           // QMATMUL: no scales; the single output holds acc - src_zp * colsum(w) as s32
   // SDPA
   int64_t batch = 0, heads = 0, seq = 0, dim = 0;
   float scale = 1.f;

@@ -320,11 +320,13 @@ struct gcb200_tp_mlp {
   // Runs `body` (which enqueues on `s`) eagerly the first time a key is seen, captures it into a CUDA graph the
   // second time and replays the graph from then on: a step is 3 launches per layer pair whose host cost would
   // otherwise exceed their device time.
+  // `body(stream)` enqueues on the stream it is given.  The capture runs on the plan's own stream (the legacy default
+  // stream cannot be captured, and a caller's stream is left alone); the finished graph is launched on `s`.
   template <class F> void run_cached(const void *a, const void *b, int mode, cudaStream_t s, F &&body) {
     static const bool graphs_on = [] { const char *e = std::getenv("GC_B200_TP_GRAPH"); return !(e && e[0] == '0'); }();
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(s, &cs) != cudaSuccess) { cudaGetLastError(); cs = cudaStreamCaptureStatusActive; }
-    if (!graphs_on || cs != cudaStreamCaptureStatusNone) { body(); return; }
+    if (s != nullptr && cudaStreamIsCapturing(s, &cs) != cudaSuccess) { cudaGetLastError(); cs = cudaStreamCaptureStatusActive; }
+    if (!graphs_on || cs != cudaStreamCaptureStatusNone) { body(s); return; }
     Graph *g = nullptr;
     for (Graph &c : graphs)
       if (c.a == a && c.b == b && c.mode == mode) g = &c;
@@ -339,16 +341,17 @@ struct gcb200_tp_mlp {
     }
     if (g->unusable || !g->seen_once) {
       g->seen_once = true;
-      body();
+      body(s);
       return;
     }
     if (!g->exec) {
       const unsigned long long l0 = launch_count();
       cudaGraph_t graph = nullptr;
-      bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+      cudaStream_t cap = stream;
+      bool ok = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
       if (ok) {
-        try { body(); } catch (...) { ok = false; }
-        if (cudaStreamEndCapture(s, &graph) != cudaSuccess || !graph) ok = false;
+        try { body(cap); } catch (...) { ok = false; }
+        if (cudaStreamEndCapture(cap, &graph) != cudaSuccess || !graph) ok = false;
       }
       if (ok && cudaGraphInstantiate(&g->exec, graph, 0) != cudaSuccess) ok = false;
       if (graph) cudaGraphDestroy(graph);
@@ -359,7 +362,7 @@ struct gcb200_tp_mlp {
         if (g->exec) cudaGraphExecDestroy(g->exec);
         g->exec = nullptr;
         g->unusable = true;
-        body();
+        body(s);
         return;
       }
       g->kernels = n;
@@ -459,7 +462,7 @@ GCB_EXPORT int gcb200_tp_mlp_step(gcb200_tp_mlp *t, const void *x, void *stream_
     std::lock_guard<std::mutex> g(t->mu);
     t->prepare();
     cudaStream_t s = static_cast<cudaStream_t>(stream_);
-    t->run_cached(x, nullptr, 0, s, [&] { t->enqueue_step(x, false, s); });
+    t->run_cached(x, nullptr, 0, s, [&](cudaStream_t q) { t->enqueue_step(x, false, q); });
     if (result) *result = t->result();
     return GCB200_OK;
   } catch (...) {
@@ -477,14 +480,14 @@ GCB_EXPORT int gcb200_tp_mlp_execute(gcb200_tp_mlp *t, const void *x_host, void 
     DeviceState &d = device_state();
     const size_t slice = size_t(t->rows()) * size_t(t->hidden[0]) * 2, off = size_t(t->rank) * slice;
     const size_t out_bytes = size_t(t->M) * size_t(t->hidden.back()) * 2;
-    t->run_cached(x_host, y_host, 1, s, [&] {
+    t->run_cached(x_host, y_host, 1, s, [&](cudaStream_t q) {
       // this rank brings only its row block over its own PCIe link; the other blocks arrive over NVLink
       GCB_CUDA(cudaMemcpyAsync(static_cast<uint8_t *>(t->x_in[size_t(t->rank)]) + off, static_cast<const uint8_t *>(x_host) + off, slice,
-                               cudaMemcpyHostToDevice, s));
-      t->enqueue_scatter(s);
-      t->enqueue_step(t->x_in[size_t(t->rank)], true, s);
-      if (y_host) GCB_CUDA(cudaMemcpyAsync(y_host, t->result(), out_bytes, cudaMemcpyDeviceToHost, s));
-      GCB_CUDA(cudaMemcpyAsync(t->host_code, d.d_error, sizeof(int), cudaMemcpyDeviceToHost, s));
+                               cudaMemcpyHostToDevice, q));
+      t->enqueue_scatter(q);
+      t->enqueue_step(t->x_in[size_t(t->rank)], true, q);
+      if (y_host) GCB_CUDA(cudaMemcpyAsync(y_host, t->result(), out_bytes, cudaMemcpyDeviceToHost, q));
+      GCB_CUDA(cudaMemcpyAsync(t->host_code, d.d_error, sizeof(int), cudaMemcpyDeviceToHost, q));
     });
     GCB_CUDA(cudaStreamSynchronize(s));
     const int code = *t->host_code;

@@ -220,6 +220,9 @@ def ref_run(fn: mlir_text.Func, tensors: Dict[str, torch.Tensor]) -> List[torch.
             env[op.out] = torch.pow(x[0], op.attrs["beta"])
         elif op.name == "reduce_sum":
             env[op.out] = torch.sum(x[0], dim=list(op.attrs["axes"]))
+        elif op.name == "qmatmul":
+            # exact in f64: |sum| < 2^53
+            env[op.out] = torch.matmul(x[0].double() - float(op.attrs["src_zp"]), x[1].double()).to(torch.int32)
         elif op.name == "softmax":
             env[op.out] = torch.softmax(x[0], op.attrs["dimension"])
         elif op.name == "batch_matmul":
@@ -286,11 +289,14 @@ def main(argv=None) -> int:
         fail, mistrust = False, False
         for j, (r, o) in enumerate(zip(ref, outs)):
             a = args[len(fn.args) + j]
-            if a.cmp_type != "P":
+            if a.cmp_type == "N":
+                ok, mis = compat.norm(float(a.cmp_param[0]), r, o)
+            elif a.cmp_type == "P":
+                if flags.verbose >= COMPARE_VERBOSE:
+                    print(f"p2p check: threshold: {float(a.cmp_param[0]):.7f}")
+                ok, mis = compat.p2p(float(a.cmp_param[0]), float(a.cmp_param[1]), r, o)
+            else:
                 raise mlir_text.Unimplemented(f"compare type {a.cmp_type}")
-            if flags.verbose >= COMPARE_VERBOSE:
-                print(f"p2p check: threshold: {float(a.cmp_param[0]):.7f}")
-            ok, mis = compat.p2p(float(a.cmp_param[0]), float(a.cmp_param[1]), r, o)
             fail |= not ok
             mistrust |= bool(mis)
         name = f"{flags.driver}.{flags.case}"

@@ -81,6 +81,16 @@ def p2p(threshold: float, zero_percent: float, ref: torch.Tensor, res: torch.Ten
     return False, None
 
 
+def norm(threshold: float, ref: torch.Tensor, res: torch.Tensor) -> Tuple[bool, bool | None]:
+    """Norm check, the harness's other comparison (test/benchgc/src/benchgc/arg/compare.py:42-57, ``--cmp i:N:threshold``):
+    sqrt(sum (ref - res)^2 / sum ref^2) < threshold, evaluated in f32."""
+    r, s = ref.to(torch.float32), res.to(torch.float32)
+    if r.nelement() == 0:
+        return True, None
+    l2 = torch.sqrt(torch.square(r - s).sum() / torch.square(r).sum()).item()
+    return l2 < threshold, None
+
+
 def max_errors(ref: torch.Tensor, res: torch.Tensor) -> Tuple[float, float]:
     """(max abs error, max rel error over |ref| > 1e-5) — reported per config."""
     r, s = ref.to(torch.float32), res.to(torch.float32)

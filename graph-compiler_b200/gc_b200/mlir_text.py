@@ -34,6 +34,7 @@ class ParseError(Exception):
 
 
 _MLIR_DTYPES = {"f32": "f32", "bf16": "bf16", "f16": "f16", "i8": "s8", "si8": "s8", "ui8": "u8", "i32": "s32", "si32": "s32"}
+_INT_DTYPES = ("s8", "u8", "s32")
 
 
 @dataclass
@@ -351,6 +352,27 @@ def parse_module(text: str, entry: str = "entry") -> Func:
             get(ins[0])
             ops.append(Op("softmax", ins, res, {"dimension": int(d.group(1))}))
             values[res] = Value(res, ot[0], "op")
+        elif opname == "linalg.quantized_matmul":
+            # C[m,n] (+)= sum_k (A[m,k] - a_zp) * (B[k,n] - b_zp) in i32; here A is ui8 (u8 activations with their zero
+            # point), B is i8 with a zero zero-point (symmetric weights): BASELINE's int8 configuration
+            ins, it = _operands(_clause(rhs, "ins"))
+            outs, ot = _operands(_clause(rhs, "outs"))
+            if len(ins) != 4:
+                raise ParseError("linalg.quantized_matmul takes A, B and the two zero points")
+            for n in ins:
+                get(n)
+            azp, bzp = get(ins[2]), get(ins[3])
+            if azp.kind != "const" or bzp.kind != "const":
+                raise Unimplemented("quantized_matmul with zero points that are not constants")
+            if int(bzp.const) != 0 or it[0].dtype != "u8" or it[1].dtype != "s8" or ot[0].dtype != "s32":
+                raise Unimplemented("quantized_matmul is taken as ui8 x i8 -> i32 with a zero weight zero-point")
+            if get(outs[0]).kind != "zero_fill":
+                raise Unimplemented("linalg.quantized_matmul whose init operand is not a zero fill")
+            a, b = it[0], it[1]
+            if a.rank != 2 or b.rank != 2 or a.shape[1] != b.shape[0] or ot[0].shape != (a.shape[0], b.shape[1]):
+                raise ParseError(f"quantized_matmul shapes do not agree: {a.shape} x {b.shape} -> {ot[0].shape}")
+            ops.append(Op("qmatmul", ins[:2], res, {"src_zp": int(azp.const)}))
+            values[res] = Value(res, ot[0], "op")
         elif opname in _BATCH_MATMUL:
             ins, it = _operands(_clause(rhs, "ins"))
             outs, ot = _operands(_clause(rhs, "outs"))
@@ -384,19 +406,19 @@ _KIND = {"add": "Add", "sub": "Subtract", "mul": "Multiply", "div": "Divide", "r
          "neg": "Negate", "exp": "Exp", "cast": "Typecast", "reshape": "StaticReshape", "pow": "Pow", "reduce_sum": "ReduceSum"}
 
 
-def _fuse_attention(fn: Func) -> List[Op]:
+def _fuse_attention(fn: Func, ops: List[Op]) -> List[Op]:
     """batch_matmul_transpose_b(Q, K) [-> mul by a splat scale] -> softmax over the last dimension -> batch_matmul(., V),
     every intermediate used once: one fused attention op (softmax as DecomposeAggregatedOps.cpp:24-38 defines it)."""
     uses: Dict[str, int] = {}
-    for op in fn.ops:
+    for op in ops:
         for n in op.ins:
             uses[n] = uses.get(n, 0) + 1
     for r in fn.results:
         uses[r] = uses.get(r, 0) + 1
-    by_out = {op.out: op for op in fn.ops}
+    by_out = {op.out: op for op in ops}
     out: List[Op] = []
     dead = set()
-    for op in fn.ops:
+    for op in ops:
         if op.name != "batch_matmul" or op.attrs["transpose_a"] or op.attrs["transpose_b"]:
             continue
         sm = by_out.get(op.ins[0])
@@ -420,13 +442,61 @@ def _fuse_attention(fn: Func) -> List[Op]:
             raise Unimplemented("attention with different Q, K and V shapes")
         dead.update({cur.out, sm.out})
         op.name, op.ins, op.attrs = "sdpa", [q, k, v], {"scale": scale}
-    for op in fn.ops:
+    for op in ops:
         if op.out not in dead:
             out.append(op)
     for op in out:
         if op.name in ("softmax", "batch_matmul"):
             raise Unimplemented(f"{op.name} outside the fused attention pattern")
     return out
+
+
+def _fuse_dequant(fn: Func, ops: List[Op]) -> List[Op]:
+    """qmatmul -> copy to f32 -> mul by a broadcast [N] scale argument [-> add a broadcast [N] bias argument], each
+    intermediate used once: one QuantizedMatMul with per-channel dequantisation (the epilogue of the int8 kernel)."""
+    uses: Dict[str, int] = {}
+    for op in ops:
+        for n in op.ins:
+            uses[n] = uses.get(n, 0) + 1
+    for r in fn.results:
+        uses[r] = uses.get(r, 0) + 1
+    consumer = {}
+    for op in ops:
+        for n in op.ins:
+            consumer.setdefault(n, op)
+
+    def channel_vector(name: str, n: int) -> Optional[str]:
+        v = fn.values[name]
+        if v.kind == "bcast" and fn.values[v.src].kind == "arg" and fn.values[v.src].type.shape == (n,) and v.bdims == (0,):
+            return v.src
+        return None
+
+    dead = set()
+    for op in ops:
+        if op.name != "qmatmul" or uses.get(op.out, 0) != 1:
+            continue
+        n = fn.values[op.out].type.shape[1]
+        cast = consumer.get(op.out)
+        if not cast or cast.name != "cast" or fn.values[cast.out].type.dtype != "f32" or uses.get(cast.out, 0) != 1:
+            continue
+        mul = consumer.get(cast.out)
+        if not mul or mul.name != "mul":
+            continue
+        other = mul.ins[1] if mul.ins[0] == cast.out else mul.ins[0]
+        scale = channel_vector(other, n)
+        if scale is None:
+            continue
+        final, bias = mul, None
+        add = consumer.get(mul.out) if uses.get(mul.out, 0) == 1 else None
+        if add and add.name == "add":
+            o2 = add.ins[1] if add.ins[0] == mul.out else add.ins[0]
+            b = channel_vector(o2, n)
+            if b is not None:
+                final, bias = add, b
+                dead.add(mul.out)
+        dead.update({op.out, cast.out})
+        final.name, final.ins, final.attrs = "qmatmul_dequant", op.ins + [scale] + ([bias] if bias else []), dict(op.attrs)
+    return [op for op in ops if op.out not in dead]
 
 
 def to_partition(fn: Func):
@@ -480,13 +550,17 @@ def to_partition(fn: Func):
             raise ParseError(f"{name} is used before it is produced")
         return {"id": ids[name], "dtype": v.type.dtype, "shape": list(v.type.shape)}
 
-    for op in _fuse_attention(fn):
+    # the fusion passes rewrite ops: work on copies, the parsed function stays as the text said
+    work = [Op(o.name, list(o.ins), o.out, dict(o.attrs)) for o in fn.ops]
+    for op in _fuse_dequant(fn, _fuse_attention(fn, work)):
         ins = [tensor(n) for n in op.ins]
         ids[op.out] = fresh()
         out = tensor(op.out)
         if op.name == "matmul":
             attrs = {a: {"type": "bool", "value": 1} for a in ("transpose_a", "transpose_b") if op.attrs[a]}
             node("MatMul", ins, [out], attrs)
+        elif op.name in ("qmatmul", "qmatmul_dequant"):
+            node("QuantizedMatMul", ins, [out], {"src_zp": {"type": "s64", "value": int(op.attrs["src_zp"])}})
         elif op.name == "sdpa":
             node("SDPA", ins, [out], {"scale": {"type": "f32", "value": op.attrs["scale"]}, "causal": {"type": "bool", "value": 0}})
         elif op.name in ("add", "sub", "mul", "div"):
@@ -697,3 +771,26 @@ def attention_module(batch_heads: int, seq: int, dim: int, scale: float, entry: 
         f"    %8 = linalg.fill ins(%cst : bf16) outs(%7 : {t}) -> {t}",
         f"    %9 = linalg.batch_matmul ins(%6, %arg2 : {ts}, {t}) outs(%8 : {t}) -> {t}",
         f"    return %9 : {t}", "  }", "}"]) + "\n"
+
+
+def quantized_matmul_module(M: int, N: int, K: int, src_zp: int = 128, dequant: bool = True, bias: bool = True, entry: str = "entry") -> str:
+    """BASELINE's int8 configuration in linalg form: ui8 activations (zero point ``src_zp``) times i8 weights with
+    linalg.quantized_matmul into i32, then (``dequant``) a cast to f32, per-output-channel scales and a bias."""
+    ta, tb, tc, tf, tv = _ty((M, K), "u8"), _ty((K, N), "s8"), _ty((M, N), "s32"), _ty((M, N), "f32"), _ty((N,), "f32")
+    sig = f"%arg0: {ta}, %arg1: {tb}" + (f", %arg2: {tv}" if dequant else "") + (f", %arg3: {tv}" if dequant and bias else "")
+    L = ["module {", f"  func.func @{entry}({sig}) -> {tf if dequant else tc} attributes {{llvm.emit_c_interface}} {{",
+         "    %c0_i32 = arith.constant 0 : i32", f"    %c{src_zp}_i32 = arith.constant {src_zp} : i32" if src_zp else "",
+         f"    %0 = tensor.empty() : {tc}", f"    %1 = linalg.fill ins(%c0_i32 : i32) outs(%0 : {tc}) -> {tc}",
+         f"    %2 = linalg.quantized_matmul ins(%arg0, %arg1, %c{src_zp}_i32, %c0_i32 : {ta}, {tb}, i32, i32) outs(%1 : {tc}) -> {tc}"]
+    res = "%2"
+    if dequant:
+        L += [f"    %3 = tensor.empty() : {tf}", f"    %4 = linalg.copy ins(%2 : {tc}) outs(%3 : {tf}) -> {tf}",
+              f"    %5 = tensor.empty() : {tf}", f"    %broadcasted = linalg.broadcast ins(%arg2 : {tv}) outs(%5 : {tf}) dimensions = [0]",
+              f"    %6 = tensor.empty() : {tf}", f"    %7 = linalg.mul ins(%4, %broadcasted : {tf}, {tf}) outs(%6 : {tf}) -> {tf}"]
+        res = "%7"
+        if bias:
+            L += [f"    %8 = tensor.empty() : {tf}", f"    %broadcasted_0 = linalg.broadcast ins(%arg3 : {tv}) outs(%8 : {tf}) dimensions = [0]",
+                  f"    %9 = tensor.empty() : {tf}", f"    %10 = linalg.add ins(%7, %broadcasted_0 : {tf}, {tf}) outs(%9 : {tf}) -> {tf}"]
+            res = "%10"
+    L += [f"    return {res} : {tf if dequant else tc}", "  }", "}"]
+    return "\n".join(x for x in L if x) + "\n"

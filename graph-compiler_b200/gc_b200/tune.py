@@ -46,6 +46,16 @@ def candidates(M: int, N: int, K: int, dtype_bytes: int = 2, out_bytes: int = 2,
         c = lib.MatmulConfig(base.swapped, bn, splits, 8 if kpb == 1 else 3, base.group_m, min(tiles * splits, sms), 0, kpb)
         out.append(c)
         seen.add((bn, splits, kpb))
+    if not base.swapped and dtype_bytes == 2 and M >= 256:
+        # the CTA-pair kernel (256 x bn tiles on two SMs) with and without a K split, whichever the model chose
+        have = {(c.bn, c.splits, max(c.kpb, 1), c.pair) for c in out}
+        for pair in (0, 1):
+            for splits in sorted({1, 2, base.splits}):
+                if splits > 1 and (k_blocks < 16 * splits or tiles_m * -(-N // 256) >= sms):
+                    continue
+                if (256, splits, 1, pair) not in have:
+                    out.append(lib.MatmulConfig(0, 256, splits, 8, base.group_m, min(tiles_m * -(-N // 256) * splits, sms), pair, 1))
+                    have.add((256, splits, 1, pair))
     return out
 
 

@@ -181,3 +181,35 @@ def test_attention_in_linalg_form_becomes_one_fused_partition():
     lone = text.replace("linalg.batch_matmul ins(%6, %arg2", "linalg.batch_matmul ins(%4, %arg2")
     with pytest.raises(mlir_text.Unimplemented):
         mlir_text.to_partition(mlir_text.parse_module(lone))
+
+
+def test_int8_matmul_in_linalg_form_becomes_one_quantized_partition():
+    """linalg.quantized_matmul on ui8 activations and i8 weights, cast, per-channel scales and bias: BASELINE's int8
+    configuration as a module; the chain folds into one QuantizedMatMul, the bare op gives its i32 accumulators."""
+    text = mlir_text.quantized_matmul_module(64, 48, 32, src_zp=128)
+    fn = mlir_text.parse_module(text)
+    assert [o.name for o in fn.ops] == ["qmatmul", "cast", "mul", "add"]
+    js, arg_ids, out_ids, consts = mlir_text.to_partition(fn)
+    g = json.loads(js)
+    assert [n["kind"] for n in g["graph"]] == ["QuantizedMatMul"] and consts == {}
+    node = g["graph"][0]
+    assert [t["dtype"] for t in node["inputs"]] == ["u8", "s8", "f32", "f32"] and node["attrs"]["src_zp"]["value"] == 128
+    assert node["outputs"][0]["dtype"] == "f32" and g["input_ports"] == [0, 1, 2, 3]
+    # the host interpretation: exact integer accumulators, then f32 arithmetic
+    torch.manual_seed(0)
+    t = {"%arg0": torch.randint(0, 256, (64, 32), dtype=torch.uint8), "%arg1": torch.randint(-127, 128, (32, 48), dtype=torch.int8),
+         "%arg2": torch.rand(48) * 0.01, "%arg3": torch.rand(48)}
+    (got,) = benchgc.ref_run(fn, t)
+    acc = (t["%arg0"].int() - 128) @ t["%arg1"].int()
+    assert torch.equal(got, acc.float() * t["%arg2"] + t["%arg3"])
+    from gc_b200 import api
+    assert "QuantizedMatMul" in api.GraphCompiler().compile(js).plan()
+    # accumulators only
+    fn2 = mlir_text.parse_module(mlir_text.quantized_matmul_module(64, 48, 32, src_zp=128, dequant=False))
+    js2, _, _, _ = mlir_text.to_partition(fn2)
+    g2 = json.loads(js2)
+    assert [n["kind"] for n in g2["graph"]] == ["QuantizedMatMul"] and g2["graph"][0]["outputs"][0]["dtype"] == "s32"
+    assert len(g2["graph"][0]["inputs"]) == 2
+    assert "QuantizedMatMul" in api.GraphCompiler().compile(js2).plan()
+    (acc2,) = benchgc.ref_run(fn2, t)
+    assert torch.equal(acc2, acc)

@@ -99,7 +99,7 @@ def test_candidates_start_with_the_model_and_respect_the_kernels_limits():
         cands = tune.candidates(*shape)
         M, N, K, eb, ob = shape
         assert _cfg(cands[0]) == _cfg(lib.model_matmul_config(*shape))
-        assert len({(c.bn, c.splits, c.kpb) for c in cands}) == len(cands)
+        assert len({(c.bn, c.splits, c.kpb, c.pair) for c in cands}) == len(cands)
         k_blocks = -(-K // (128 // eb))
         for c in cands[1:]:
             assert c.swapped == cands[0].swapped and 1 <= c.grid <= 148
