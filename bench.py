@@ -522,6 +522,9 @@ def main():
     ap.add_argument("--no-sweep", dest="sweep", action="store_false", help="headline workload only (profiling runs)")
     ap.add_argument("--case", default=None, help="time ONE kernel-level case instead (see run_case) and print its line; "
                                                   "used for ncu captures of a single kernel")
+    ap.add_argument("--tp-timeline", action="store_true",
+                    help="under torchrun: print, per rank-0 kernel of one eagerly launched tensor-parallel step, the time it took "
+                         "(CUDA events between the launches; waits for other ranks included), instead of the bench line")
     ap.add_argument("--flush", default="auto", choices=["auto", "on", "off"],
                     help="--case only: write a 256 MiB buffer between timed launches (auto: when the working set is below 256 MB)")
     a = ap.parse_args()
@@ -620,6 +623,24 @@ def main():
         tpf = FusedTensorParallelMLP(ws, bs, BATCH, HIDDEN, dev, relu=True)
         Xd = X_host.to(dev)
         holder = {}
+
+        if a.tp_timeline:
+            for _ in range(a.warmup):
+                tpf.step(Xd)
+            torch.cuda.synchronize()
+            dist.barrier()
+            lines = []
+            for _ in range(max(1, min(a.steps, 5))):
+                lines.append(tpf.plan.timeline(Xd.data_ptr()))
+            if rank == 0:
+                print(f"tp{world} MLP step, rank 0, last of {len(lines)} eagerly launched steps (microseconds from the end of the "
+                      "launch before to the end of this one):")
+                print(lines[-1])
+            assert lib.device_error() == 0
+            dist.barrier()
+            tpf.close()
+            dist.destroy_process_group()
+            return
 
         def step_device():
             holder["y"] = tpf.step(Xd)

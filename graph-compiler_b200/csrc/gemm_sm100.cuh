@@ -80,6 +80,7 @@ struct GemmParams {
   const uint32_t *wait_counter;
   const uint32_t *epoch;
   uint32_t wait_per_step;
+  int park_epilogue;    // 1: the epilogue warps wait for their accumulator with the suspend-time hint (parked) instead of polling
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
   // TMA-store epilogue (one-CTA kernel, row-major orientation): tmC covers the output as
   // [planes][rows][cols] with a box of {128 bytes of columns, 32 rows, 1}; each epilogue warp hands its

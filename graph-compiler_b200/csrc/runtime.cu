@@ -338,6 +338,10 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   p.out_rows = int(a.M);
   p.out_cols = int(a.N);
   p.error = dev.d_error;
+  {
+    static const int park = [] { const char *e = std::getenv("GC_B200_PARK"); return (e && e[0] == '1') ? 1 : 0; }();
+    p.park_epilogue = park;
+  }
 
   // operand roles in MMA orientation
   const void *pa, *pb;

@@ -176,6 +176,11 @@ struct gcb200_tp_mlp {
   size_t splitk_bytes = 0;
   cudaStream_t stream = nullptr; // host-buffer path
   int *host_code = nullptr;
+  // optional timeline of one eagerly launched step: an event after every launch (see gcb200_tp_mlp_timeline)
+  std::vector<cudaEvent_t> marks;
+  std::vector<std::string> mark_names;
+  size_t marks_used = 0;
+  bool timeline = false;
   std::vector<MatmulConfig> row_cfg;   // configuration of every row-parallel layer (fixes the arrival counts)
   std::vector<int> row_arrivals;
   struct Graph {
@@ -191,7 +196,20 @@ struct gcb200_tp_mlp {
   int exchanges() const { return layers / 2; }
   uint32_t *counter(int rank_, int word) const { return sig[size_t(rank_)] + word; }
 
+  void mark(const char *name, cudaStream_t s) {
+    if (!timeline) return;
+    if (marks_used == marks.size()) {
+      cudaEvent_t e = nullptr;
+      GCB_CUDA(cudaEventCreate(&e));
+      marks.push_back(e);
+      mark_names.emplace_back();
+    }
+    mark_names[marks_used] = name;
+    GCB_CUDA(cudaEventRecord(marks[marks_used++], s));
+  }
+
   ~gcb200_tp_mlp() {
+    for (cudaEvent_t e : marks) cudaEventDestroy(e);
     for (Graph &g : graphs)
       if (g.exec) cudaGraphExecDestroy(g.exec);
     for (void *p : col_out)
@@ -245,6 +263,8 @@ struct gcb200_tp_mlp {
     DeviceState &d = device_state();
     const uint32_t *step_word = counter(rank, SIG_STEP);
     const void *h = x;
+    marks_used = 0;
+    mark("start", s);
     for (int e = 0; e < exchanges(); ++e) {
       const int64_t Kc = hidden[size_t(2 * e)], Nc = hidden[size_t(2 * e + 1)] / world, Nr = hidden[size_t(2 * e + 2)];
       {   // column-parallel layer: local bias / ReLU; its input rows come from the other ranks (except the first layer's)
@@ -263,6 +283,7 @@ struct gcb200_tp_mlp {
           m.epoch = step_word;
         }
         matmul_tc(m, s);
+        mark("column-parallel gemm (+ wait for the previous exchange's rows)", s);
       }
       {   // row-parallel layer: f32 partial sums scattered by rows from the GEMM epilogue, counted in at the owner
         void *bufs[kMaxRanks];
@@ -278,6 +299,7 @@ struct gcb200_tp_mlp {
         m.arrivals_per_peer = &arrivals;
         matmul_tc(m, s);
         if (arrivals != row_arrivals[size_t(e)]) throw std::logic_error("row-parallel layer ran with an unplanned tile configuration");
+        mark("row-parallel gemm + row scatter to the owners", s);
       }
       {   // this rank's rows: reduce, epilogue, all-gather by peer stores
         PeerRows pr{};
@@ -291,12 +313,14 @@ struct gcb200_tp_mlp {
                    reinterpret_cast<const uint2 *>(B[size_t(2 * e + 1)]), relu, pr, world, (long long)(rank * total4),
                    reinterpret_cast<const uint32_t *>(counter(rank, SIG_PART0 + e)), uint32_t(world * row_arrivals[size_t(e)]), step_word,
                    d.d_error);
+        mark("wait for all ranks' partial sums + reduce + all-gather stores", s);
       }
       h = act[e & 1][size_t(rank)];
     }
     const int last = exchanges() - 1;
     launch_pdl(tp_step_end_kernel, dim3(1), dim3(32), s, reinterpret_cast<const uint32_t *>(counter(rank, SIG_ROWS0 + last)),
                uint32_t(world * reduce_blocks(rows(), hidden.back())), counter(rank, SIG_STEP), d.d_error);
+    mark("wait for every owner's rows (end of step)", s);
   }
 
   int scatter_blocks() const {
@@ -495,6 +519,43 @@ GCB_EXPORT int gcb200_tp_mlp_execute(gcb200_tp_mlp *t, const void *x_host, void 
       GCB_CUDA(cudaMemset(d.d_error, 0, sizeof(int)));
       *t->host_code = 0;
       throw CudaError("a kernel gave up a bounded wait (code " + std::to_string(code) + ")");
+    }
+    return GCB200_OK;
+  } catch (...) {
+    return guard_status(std::current_exception());
+  }
+}
+
+GCB_EXPORT int gcb200_tp_mlp_timeline(gcb200_tp_mlp *t, const void *x, void *stream_, char *buf, size_t cap, size_t *needed) {
+  try {
+    if (!t || !x) throw std::invalid_argument("null argument");
+    std::lock_guard<std::mutex> g(t->mu);
+    t->prepare();
+    cudaStream_t s = static_cast<cudaStream_t>(stream_);
+    t->timeline = true;
+    try {
+      t->enqueue_step(x, false, s);   // eager launches with an event behind each
+    } catch (...) {
+      t->timeline = false;
+      throw;
+    }
+    t->timeline = false;
+    GCB_CUDA(cudaStreamSynchronize(s));
+    std::ostringstream os;
+    for (size_t i = 1; i < t->marks_used; ++i) {
+      float ms = 0.f;
+      GCB_CUDA(cudaEventElapsedTime(&ms, t->marks[i - 1], t->marks[i]));
+      os << ms * 1e3f << " us  " << t->mark_names[i] << "\n";
+    }
+    float total = 0.f;
+    if (t->marks_used > 1) GCB_CUDA(cudaEventElapsedTime(&total, t->marks[0], t->marks[t->marks_used - 1]));
+    os << total * 1e3f << " us  whole step (eager launches; a replayed graph has no launch gaps)\n";
+    const std::string str = os.str();
+    if (needed) *needed = str.size() + 1;
+    if (buf && cap) {
+      const size_t n = std::min(cap - 1, str.size());
+      std::memcpy(buf, str.data(), n);
+      buf[n] = '\0';
     }
     return GCB200_OK;
   } catch (...) {

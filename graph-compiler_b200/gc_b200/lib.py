@@ -87,6 +87,7 @@ def load() -> C.CDLL:
         "gcb200_tp_mlp_describe": [_vp, _int, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)],
         "gcb200_tp_mlp_step": [_vp, _vp, _vp, C.POINTER(_vp)],
         "gcb200_tp_mlp_execute": [_vp, _vp, _vp],
+        "gcb200_tp_mlp_timeline": [_vp, _vp, _vp, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)],
         "gcb200_wait_selftest": [C.c_longlong, _vp],
     }
     for name, argtypes in sig.items():
@@ -374,6 +375,12 @@ class TpMlpPlan:
         res = _vp(None)
         check(load().gcb200_tp_mlp_step(self._h, _vp(x_ptr), _stream() if stream is None else _vp(stream), C.byref(res)))
         return int(res.value)
+
+    def timeline(self, x_ptr: int, stream=None) -> str:
+        """One eagerly launched step with an event behind every launch: one line per kernel, microseconds first."""
+        buf = C.create_string_buffer(4096)
+        check(load().gcb200_tp_mlp_timeline(self._h, _vp(x_ptr), _stream() if stream is None else _vp(stream), buf, 4096, None))
+        return buf.value.decode()
 
     def execute(self, x_host_ptr: int, y_host_ptr: int = 0):
         check(load().gcb200_tp_mlp_execute(self._h, _vp(x_host_ptr), _vp(y_host_ptr) if y_host_ptr else _vp(None)))

@@ -293,6 +293,10 @@ int gcb200_tp_mlp_destroy(gcb200_tp_mlp *plan);
 int gcb200_tp_mlp_describe(const gcb200_tp_mlp *plan, int sm_count, char *buf, size_t cap, size_t *needed);
 int gcb200_tp_mlp_step(gcb200_tp_mlp *plan, const void *x, void *stream, void **result);
 int gcb200_tp_mlp_execute(gcb200_tp_mlp *plan, const void *x_host, void *y_host);
+/* One step launched eagerly with a CUDA event behind every launch; writes one line per kernel ("<microseconds> us
+ * <what>": the time from the end of the launch before to the end of this one, waits for other ranks included) and
+ * the total.  Synchronises `stream`.  Every rank must call it (it is a step like any other). */
+int gcb200_tp_mlp_timeline(gcb200_tp_mlp *plan, const void *x, void *stream, char *buf, size_t cap, size_t *needed);
 
 /* Failure-path self-test: launches a kernel that waits (for at most `limit_cycles` SM clock cycles, which must not
  * exceed the library's own limit) on a counter nothing ever adds to, gives up, records code 7 in the device error
