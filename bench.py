@@ -614,7 +614,9 @@ def main():
             bound.run()   # dnnl_graph_compiler_execute: H2D of X, 4 launches, D2H of the result, synchronous
 
         parallelism = "single GPU"
-    elif os.environ.get("GC_B200_EXCHANGE", "fused_counters") == "fused_counters":
+    fused_note = ""
+    use_fused = world > 1 and os.environ.get("GC_B200_EXCHANGE", "fused_counters") == "fused_counters"
+    if use_fused:
         # The tensor-parallel step behind the C ABI (gcb200_tp_mlp_*): GEMMs, exchange and every hand-off between the
         # GPUs are this library's own kernels; the step is replayed as a CUDA graph inside the library.
         from gc_b200.tensor_parallel import FusedTensorParallelMLP
@@ -623,6 +625,28 @@ def main():
         tpf = FusedTensorParallelMLP(ws, bs, BATCH, HIDDEN, dev, relu=True)
         Xd = X_host.to(dev)
         holder = {}
+        # Every rank must come through one eager step, one captured step and one host-buffer call with a clean error
+        # word; if any rank does not (a bounded wait ran out), all ranks fall back to the Python-driven exchange.
+        ok = 1
+        try:
+            for _ in range(2):
+                tpf.step(Xd)
+            torch.cuda.synchronize()
+            tpf.execute(X_host, None)
+            ok = 1 if lib.device_error() == 0 else 0
+        except Exception as e:
+            ok, fused_note = 0, f"{type(e).__name__}: {e}"[:160]
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            use_fused = False
+            fused_note = "fused tensor-parallel step failed its self-check on some rank" + (f" ({fused_note})" if fused_note else "")
+            try:
+                tpf.close()
+            except Exception:
+                pass
+
+    if world > 1 and use_fused:
 
         if a.tp_timeline:
             for _ in range(a.warmup):
@@ -653,17 +677,19 @@ def main():
         parallelism = (f"tp{world} behind the C ABI: row-parallel partial sums leave the GEMM epilogue for the rank that owns the rows "
                        "(peer stores), the owner reduces and stores the bf16 rows to every rank; hand-offs are device counters of "
                        "this library's kernels; one CUDA-graph replay per step")
-    else:
+    elif world > 1:
         from gc_b200.tensor_parallel import AllReduceExchange, CudaOps, PeerPushExchange, PeerReduceScatterExchange
 
         ws, bs = shard_weights([w.to(dev) for w in W_host], [b.to(dev) for b in B_host], world, rank)
-        exchange, why = None, ""
+        exchange, why = None, (" [" + fused_note + "]" if fused_note else "")
         # fused GEMM-epilogue exchanges: with two ranks sending the whole tile to the one peer is already minimal;
         # beyond that the partial sums are reduce-scattered by rows and the result all-gathered
         # every partial sum to every rank costs (g - 1) x 8 MiB of NVLink stores per rank and exchange: best at two ranks
         # (211 us per step against 228); the reduce-scatter form moves an all-reduce's traffic and wins beyond
         # (4 ranks: 171 us against 203; 8 ranks: 145 us against 289)
-        want = os.environ.get("GC_B200_EXCHANGE", "peer_push" if world <= 2 else "peer_reduce_scatter")
+        want = os.environ.get("GC_B200_EXCHANGE", "fused_counters")
+        if want == "fused_counters":
+            want = "peer_push" if world <= 2 else "peer_reduce_scatter"
         if want in ("peer_push", "peer_push_multicast", "peer_reduce_scatter"):
             try:
                 if want == "peer_reduce_scatter":

@@ -45,6 +45,12 @@ __device__ __forceinline__ void pair_tile_coords(const GemmParams &p, int tile, 
   tn = r / gsz;
 }
 
+// Bounded wait until this step's rows of the activations (stored by other GPUs' kernels) have landed here.
+__device__ __forceinline__ bool pair_rows_landed(const GemmParams &p) {
+  const uint32_t target = (*reinterpret_cast<const volatile uint32_t *>(p.epoch) + 1u) * p.wait_per_step;
+  return wait_counter_reached(p.wait_counter, target, 4 * WAIT_LIMIT_CYCLES);
+}
+
 // p.tiles_m counts 256-row tiles; p.b describes this CTA's half (BN/2 columns) of the B tile.
 template <int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
@@ -106,6 +112,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool mn = g.mn_major != 0, one = g.one_load != 0;
       const int bk = p.bk_elems;
       int err = 0;
+      // see gemm_sm100.cu: the activation producer waits for this step's rows before its first load, the weight
+      // producer after it has filled the ring
+      const bool gated = p.wait_counter != nullptr;
+      bool gate_open = !gated;
+      uint32_t issued = 0;
+      auto peer_gate = [&]() {
+        if (!pair_rows_landed(p)) err = ERR_WAIT_PEER;
+        fence_proxy_async_global();
+        gate_open = true;
+      };
+      if (gated && is_a) peer_gate();
       for (int u = pair; u < units && !err; u += pairs) {
         const int tile = u / p.splits, split = u - tile * p.splits;
         int tm_, tn_;
@@ -114,7 +131,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int kb0 = split * kb_per_split, kb1 = min(p.k_blocks, kb0 + kb_per_split);
         int k_off = kb0 * bk;
         const int grp = mn_off / int(box_mn ? box_mn : 1u);
-        for (int kb = kb0; kb < kb1; ++kb, k_off += bk) {
+        for (int kb = kb0; kb < kb1; ++kb, k_off += bk, ++issued) {
+          if (!gate_open && issued >= uint32_t(stages)) { peer_gate(); if (err) break; }
           if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u)) { err = ERR_WAIT_EMPTY; break; }
           const uint32_t full = smem_u32(&bars->full[s]);
           if (rank == 0) mbar_expect_tx(full, 2 * my_bytes);   // both CTAs' bytes of this operand land here
@@ -147,6 +165,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int s = 0;
       uint32_t ph = 0;
       int err = 0;
+      if (p.wait_counter != nullptr && !pair_rows_landed(p)) err = ERR_WAIT_PEER;
       for (int u = pair; u < units && !err; u += pairs, ++tcount) {
         const int tile = u / p.splits, split = u - tile * p.splits;
         const int kb0 = split * kb_per_split, kb1 = min(p.k_blocks, kb0 + kb_per_split);
@@ -185,7 +204,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t *stg = staging + (warp - 2) * kStaging2;
     uint32_t tcount = 0;
     uint32_t slab = 0;   // TMA-store form: staging slab to fill next
-    for (int u = pair; u < units; u += pairs, ++tcount) {
+    bool dead = false;
+    if (p.wait_counter != nullptr) {
+      bool ok = true;
+      if (lane == 0) ok = pair_rows_landed(p);
+      ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) atomicExch(p.error, ERR_WAIT_PEER);
+        dead = true;
+      }
+    }
+    for (int u = pair; u < units && !dead; u += pairs, ++tcount) {
       const int tile = u / p.splits, split = u - tile * p.splits;
       int tm, tn;
       pair_tile_coords(p, tile, tm, tn);

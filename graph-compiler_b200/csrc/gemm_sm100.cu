@@ -56,6 +56,12 @@ __device__ __forceinline__ void tile_coords(const GemmParams &p, int tile, int &
   tn = r / gsz;
 }
 
+// Bounded wait until this step's rows of the activations (stored by other GPUs' kernels) have landed here.
+__device__ __forceinline__ bool peer_rows_landed(const GemmParams &p) {
+  const uint32_t target = (*reinterpret_cast<const volatile uint32_t *>(p.epoch) + 1u) * p.wait_per_step;
+  return wait_counter_reached(p.wait_counter, target, 4 * WAIT_LIMIT_CYCLES);
+}
+
 template <int KIND, bool SWAPPED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -116,12 +122,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool mn = g.mn_major != 0, one = g.one_load != 0, k3d = g.k3d != 0;
       const int bk = p.bk_elems, kpb = max(p.kpb, 1);
       int err = 0;
-      if (p.wait_counter != nullptr) {
-        // the activations are stored into this GPU's memory by other GPUs' kernels: wait for this step's rows
-        const uint32_t target = (*reinterpret_cast<const volatile uint32_t *>(p.epoch) + 1u) * p.wait_per_step;
-        if (!wait_counter_reached(p.wait_counter, target)) err = ERR_WAIT_PEER;
+      // Activations that other GPUs' kernels store into this GPU's memory: their producer waits for this step's rows
+      // before its first load; the weight producer fills the ring first (weights are local) and waits before it would
+      // block on a stage the MMA thread cannot have released yet, so that no mbarrier wait of this CTA starts its
+      // clock while the rows are still on their way.
+      const bool gated = p.wait_counter != nullptr;
+      const bool is_act = (is_a != SWAPPED);
+      bool gate_open = !gated;
+      auto peer_gate = [&]() {
+        if (!peer_rows_landed(p)) err = ERR_WAIT_PEER;
         fence_proxy_async_global();
-      }
+        gate_open = true;
+      };
+      if (gated && is_act) peer_gate();
       for (int u = blockIdx.x; u < units && !err; u += gridDim.x) {
         const int tile = u / p.splits, split = u - tile * p.splits;
         int tm_, tn_;
@@ -131,6 +144,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int k_off = kb0 * bk;
         const int grp = mn_off / int(box_mn ? box_mn : 1u);   // 3-D form: index of the first 64-wide MN group
         for (int kb = kb0; kb < kb1; kb += kpb, ++it, k_off += bk * kpb) {
+          if (!gate_open && it >= uint32_t(stages)) { peer_gate(); if (err) break; }
           if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u)) { err = ERR_WAIT_EMPTY; break; }
           const uint32_t full = smem_u32(&bars->full[s]);
           mbar_expect_tx(full, my_bytes);
@@ -180,6 +194,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int s = 0;
       uint32_t ph = 0;
       int err = 0;
+      if (p.wait_counter != nullptr && !peer_rows_landed(p)) err = ERR_WAIT_PEER;
       for (int u = blockIdx.x; u < units && !err; u += gridDim.x, ++tcount) {
         const int tile = u / p.splits, split = u - tile * p.splits;
         const int kb0 = split * kb_per_split, kb1 = min(p.k_blocks, kb0 + kb_per_split);
@@ -223,6 +238,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint32_t tcount = 0;
     uint32_t slab = 0;   // TMA-store form: staging slab to fill next
     bool dead = false;
+    if (p.wait_counter != nullptr) {
+      bool ok = true;
+      if (lane == 0) ok = peer_rows_landed(p);
+      ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) atomicExch(p.error, ERR_WAIT_PEER);
+        dead = true;
+      }
+    }
     for (int u = blockIdx.x; u < units && !dead; u += gridDim.x, ++tcount) {
       const int tile = u / p.splits, split = u - tile * p.splits;
       int tm, tn;

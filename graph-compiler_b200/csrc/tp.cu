@@ -46,7 +46,9 @@ namespace {
 constexpr int kMaxRanks = 8;
 constexpr int kMaxExchanges = 6;
 // counter slots (uint32 index) inside a rank's signal block
-enum : int { SIG_STEP = 0, SIG_X_LANDED = 1, SIG_PART0 = 2, SIG_ROWS0 = 2 + kMaxExchanges, SIG_WORDS = 2 + 2 * kMaxExchanges };
+// (SIG_XSTEP counts only the steps whose input was fanned out by tp_scatter_rows_kernel: SIG_X_LANDED grows only in those)
+enum : int { SIG_STEP = 0, SIG_X_LANDED = 1, SIG_PART0 = 2, SIG_ROWS0 = 2 + kMaxExchanges, SIG_XSTEP = 2 + 2 * kMaxExchanges,
+             SIG_WORDS = 3 + 2 * kMaxExchanges };
 
 struct PeerRows {
   uint2 *out[kMaxRanks];
@@ -102,13 +104,14 @@ tp_reduce_bcast_kernel(const float4 *parts, int nparts, long long plane4, long l
 
 // Last kernel of a step: the result is complete on this rank once every owner's rows have landed; then the step
 // word moves on (plain store: the kernels of the next step come later in the same stream).
-__global__ void tp_step_end_kernel(const uint32_t *rows_landed, uint32_t per_step, uint32_t *step, int *error) {
+__global__ void tp_step_end_kernel(const uint32_t *rows_landed, uint32_t per_step, uint32_t *step, uint32_t *xstep, int *error) {
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x == 0) {
     const uint32_t n = *reinterpret_cast<volatile uint32_t *>(step);
     if (!wait_counter_reached(rows_landed, (n + 1u) * per_step, 4 * WAIT_LIMIT_CYCLES)) atomicExch(error, ERR_WAIT_PEER);
     *reinterpret_cast<volatile uint32_t *>(step) = n + 1u;
+    if (xstep) *reinterpret_cast<volatile uint32_t *>(xstep) = *reinterpret_cast<volatile uint32_t *>(xstep) + 1u;
   }
 }
 
@@ -280,7 +283,7 @@ struct gcb200_tp_mlp {
         } else if (x_scattered) {
           m.wait_counter = counter(rank, SIG_X_LANDED);
           m.wait_per_step = uint32_t(world * scatter_blocks());
-          m.epoch = step_word;
+          m.epoch = counter(rank, SIG_XSTEP);
         }
         matmul_tc(m, s);
         mark("column-parallel gemm (+ wait for the previous exchange's rows)", s);
@@ -319,7 +322,8 @@ struct gcb200_tp_mlp {
     }
     const int last = exchanges() - 1;
     launch_pdl(tp_step_end_kernel, dim3(1), dim3(32), s, reinterpret_cast<const uint32_t *>(counter(rank, SIG_ROWS0 + last)),
-               uint32_t(world * reduce_blocks(rows(), hidden.back())), counter(rank, SIG_STEP), d.d_error);
+               uint32_t(world * reduce_blocks(rows(), hidden.back())), counter(rank, SIG_STEP),
+               x_scattered ? counter(rank, SIG_XSTEP) : static_cast<uint32_t *>(nullptr), d.d_error);
     mark("wait for every owner's rows (end of step)", s);
   }
 
