@@ -522,6 +522,9 @@ def main():
     ap.add_argument("--no-sweep", dest="sweep", action="store_false", help="headline workload only (profiling runs)")
     ap.add_argument("--case", default=None, help="time ONE kernel-level case instead (see run_case) and print its line; "
                                                   "used for ncu captures of a single kernel")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="after the timed region, run the device-resident step back to back for about this long and report it "
+                         "under 'sustained' (0 = skip)")
     ap.add_argument("--tp-timeline", action="store_true",
                     help="under torchrun: print, per rank-0 kernel of one eagerly launched tensor-parallel step, the time it took "
                          "(CUDA events between the launches; waits for other ranks included), instead of the bench line")
@@ -793,6 +796,29 @@ def main():
     ms_dev, launches, sampler = timed(step_device, a.steps, a.warmup, sample_clocks=True)
     ms_e2e, _, _ = timed(step_e2e, max(3, a.steps // 2), a.warmup)
     clocks = sampler.stop()   # sampled from the start of the device-timed region to the end of the end-to-end one
+    # The timed region above is milliseconds long (a burst at full clock).  The same step back to back for about two
+    # seconds shows what the GPU holds once the power cap acts; compared with the sustained cuBLAS figure of this pool.
+    sustained = None
+    if a.sustained_seconds > 0:
+        s2 = make_clock_sampler(local_rank)
+        barrier()
+        s2.start()
+        n_s = max(a.steps, int(a.sustained_seconds * 1e3 / max(ms_dev, 1e-3)))
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.record()
+        for _ in range(n_s):
+            step_device()
+        en.record()
+        barrier()
+        ms_s = st.elapsed_time(en) / n_s
+        c2 = s2.stop()
+        if world > 1:
+            t = torch.tensor([ms_s], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_s = float(t.item())
+        sustained = {"value": flops / ms_s / 1e9, "unit": "TFLOPS", "ms_per_step": ms_s, "steps": n_s, "seconds": ms_s * n_s / 1e3,
+                     "sm_mhz_median": c2.get("sm_mhz"), "reasons": c2.get("reasons"),
+                     "ms_x_mhz": (ms_s * c2["sm_mhz"] if c2.get("sm_mhz") else None)}
     assert lib.device_error() == 0, "a kernel reported a bounded-wait time-out"
 
     # ---- the step that was timed computed the right thing: 16 rows of its output against the CPU oracle (rank 0)
@@ -823,12 +849,16 @@ def main():
         "gpu_launches": int(gemm_launches),
         "exchange": exchange_note,
         "parity": parity,
+        "sustained": sustained,
+        "ms_x_mhz": (ms_dev * clocks["sm_mhz"] if clocks.get("sm_mhz") else None),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s", "frac": achieved / peaks[peak_kind],
                      "traffic": traffic, "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind}",
                      "kernel": "gemm_kernel<bf16, f32 accumulate> (tcgen05 + TMA), incl. launch gaps",
                      "frac_of_vendor_dense_2250": achieved / 2250.0},
     }
+    if sustained is not None:
+        sustained["frac_of_measured_sustained_peak"] = sustained["value"] / world / peaks["sustained"]
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         r = cpu_reference_run(1, 0)
         line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}

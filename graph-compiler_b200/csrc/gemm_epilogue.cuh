@@ -32,6 +32,7 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
     const bool dump_vec = dump && ((size_t(p.ld_dump) & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.acc_dump) & 15) == 0);
     const int chunk = lane & 7, rsub = lane >> 3;
     const int cpc = two_byte ? 8 : 4;   // columns per 16-byte chunk
+    const int warp_owner = (p.peer_rows > 0 && (p.peer_rows & 31) == 0) ? (row0 + q * 32) / p.peer_rows : -1;
     const bool late_bf16 = two_byte && p.bias_kind == BIAS_BF16;   // bias (and ReLU) applied in the store phase
     for (int c0 = 0; c0 < p.BN; c0 += slab_cols) {
       const int col0 = nn0 + c0;
@@ -139,9 +140,13 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
           // NVLink), so the exchange overlaps the tiles still being computed.  Requires full
           // 16-byte chunks (checked by the launcher).
           if (p.peer_rows > 0) {
-            // reduce-scatter by rows: only the rank that will reduce this row receives it
-            const int owner = grow / p.peer_rows, lrow = grow - owner * p.peer_rows;
-            const size_t off = (size_t(p.peer_plane) * size_t(p.peer_rows) + size_t(lrow)) * ld_b + size_t(gcol) * esz;
+            // reduce-scatter by rows: only the rank that will reduce this row receives it (a warp's 32 rows share
+            // one owner whenever the rows per peer are a multiple of 32: one division per warp and tile then)
+            int owner = warp_owner, lrow = grow - warp_owner * p.peer_rows;
+            if (warp_owner < 0) { owner = grow / p.peer_rows; lrow = grow - owner * p.peer_rows; }
+            // one plane per (rank, K split): the owner sums them in plane order
+            const size_t pl = size_t(p.peer_plane) * size_t(p.splits) + size_t(split);
+            const size_t off = (pl * size_t(p.peer_rows) + size_t(lrow)) * ld_b + size_t(gcol) * esz;
             *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_out[owner]) + off) = val;
           } else {
             const size_t off = (size_t(p.peer_plane) * size_t(p.out_rows) + size_t(grow)) * ld_b + size_t(gcol) * esz;
@@ -171,10 +176,9 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams &p, uint32_t
     if (p.n_peers > 0 && p.peer_rows > 0 && p.signal_peer[0] != nullptr) {
       // this warp's 32 rows of the tile are on their way to their owner: make them visible system-wide, then count
       // the warp in at the owner (the owner's reduction waits for every warp of every tile of every rank)
-      __threadfence_system();
       __syncwarp();
       const int grow = row0 + q * 32;
-      if (lane == 0 && grow < p.out_rows) red_release_sys_add_u32(p.signal_peer[grow / p.peer_rows], 1u);
+      if (lane == 0 && grow < p.out_rows) publish_and_count(p.signal_peer[grow / p.peer_rows]);
     }
   } else {
   // ---- swapped orientation: MMA row = output column (this thread),
@@ -325,10 +329,16 @@ __device__ __forceinline__ void gemm_epilogue_tile_tma(const GemmParams &p, uint
   const int slab_cols = two_byte ? 64 : 32;
   const int grow0 = row0 + q * 32;
   const bool rows_in = grow0 < p.out_rows;
+  // row scatter: this warp's 32 rows belong to one owner, whose buffer has its own tensor map
+  // (tma_peer 1: row scatter to the owner; 2: the finished slab goes to EVERY rank's result - all-gather of C)
+  const int owner = p.tma_peer == 1 ? grow0 / p.peer_rows : 0;
+  const CUtensorMap *tmap = p.tma_peer == 1 ? &p.tmPeer[owner] : &p.tmC;
+  const int store_row = p.tma_peer == 1 ? grow0 - owner * p.peer_rows : grow0;
+  const int store_plane = p.tma_peer == 1 ? p.peer_plane * p.splits + split : split;
   for (int c0 = 0; c0 < p.BN; c0 += slab_cols) {
     const int col0 = nn0 + c0;
     if (col0 >= p.out_cols) break;
-    if (p.BN - c0 < slab_cols) {
+    if (p.tma_peer != 1 && p.BN - c0 < slab_cols) {
       // the tile is not a whole number of slabs wide (BN a multiple of 16 only): the last 16, 32 or 48 columns
       // go from registers straight to global memory, 16 columns (32 or 64 contiguous bytes per row) at a time
       gemm_epilogue_tail<KIND>(p, t_addr, c0, col0, grow0 + lane, split, lane);
@@ -410,10 +420,23 @@ __device__ __forceinline__ void gemm_epilogue_tile_tma(const GemmParams &p, uint
     fence_proxy_async();   // generic-proxy writes of the slab -> visible to the copy engine
     __syncwarp();
     if (lane == 0 && rows_in) {
-      tma_store_3d(&p.tmC, smem_u32(slab), col0, grow0, split);
+      if (p.tma_peer == 2) {
+        for (int d = 0; d < p.n_peers; ++d) tma_store_3d(&p.tmPeer[d], smem_u32(slab), col0, grow0, 0);
+      } else {
+        tma_store_3d(tmap, smem_u32(slab), col0, store_row, store_plane);
+      }
       tma_store_commit();
     }
     buf ^= 1u;
+  }
+  if (p.tma_peer == 1 && p.signal_peer[0] != nullptr) {
+    // the warp's rows of this tile are on their way to their owner: once the copy engine has completed the stores
+    // (not merely read the slabs), publish them and count the warp in at the owner
+    __syncwarp();
+    if (lane == 0 && rows_in) {
+      tma_store_wait<0>();
+      publish_and_count(p.signal_peer[owner]);
+    }
   }
 }
 

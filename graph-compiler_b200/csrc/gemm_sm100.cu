@@ -252,7 +252,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int tm, tn;
       tile_coords(p, tile, tm, tn);
       const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
-      if (!(p.park_epilogue ? mbar_wait_parked(smem_u32(&bars->tmem_full[acc]), acc_ph) : mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_ph))) {
+      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_ph)) {
         if (lane == 0) atomicExch(p.error, ERR_WAIT_TMEM_FULL);
         dead = true;
         break;

@@ -80,13 +80,17 @@ struct GemmParams {
   const uint32_t *wait_counter;
   const uint32_t *epoch;
   uint32_t wait_per_step;
-  int park_epilogue;    // 1: the epilogue warps wait for their accumulator with the suspend-time hint (parked) instead of polling
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
   // TMA-store epilogue (one-CTA kernel, row-major orientation): tmC covers the output as
   // [planes][rows][cols] with a box of {128 bytes of columns, 32 rows, 1}; each epilogue warp hands its
   // 32 x 128-byte slabs to the copy engine instead of storing them itself.
   int tma_store;
   CUtensorMap tmC;
+  // Row scatter through the copy engine (tma_peer = 1, with tma_store): tmPeer[d] covers owner d's receive buffer as
+  // [planes][rows per peer][cols] f32 with the same box; a warp's 32-row slab goes to its owner's buffer with one
+  // cp.async.bulk.tensor store (plain bulk stores over NVLink, no loads from a peer).
+  int tma_peer;
+  CUtensorMap tmPeer[8];
 };
 
 // KIND: 0 = bf16 x bf16 -> f32, 1 = u8 x s8 -> s32.  SWAPPED: MMA rows are output columns.

@@ -134,7 +134,8 @@ bool tma_compatible(const void *ptr, int64_t row_elems, int elem_bytes) {
 // ----------------------------------------------------------------------------- tile selection
 static int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); }
 
-MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count) {
+MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count, int max_splits) {
+  if (max_splits >= 1 && max_splits < 8) return model_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count, max_splits);
   // a configuration measured for exactly this shape beats the model; an explicit GC_B200_TILE beats both
   MatmulConfig c{};
   if (!std::getenv("GC_B200_TILE") && tune::lookup(tune::Key{M, N, K, dtype_bytes, out_bytes}, &c) && (!c.swapped || M <= 64)) {
@@ -144,7 +145,7 @@ MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byt
   return model_matmul_config(M, N, K, dtype_bytes, out_bytes, sm_count);
 }
 
-MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count) {
+MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count, int max_splits) {
   MatmulConfig c{};
   const int bk = 128 / dtype_bytes;
   const int k_blocks = ceil_div(K, bk);
@@ -174,6 +175,7 @@ MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_byte
                                                                                       : (kpb == 2 ? 0.21 : 0.29) * std::max(0.6, bn_eff / 64.0);
       const int t = ceil_div(M, 128) * ceil_div(N, bn_eff);
       for (int sp : split_cand) {
+        if (sp > max_splits) continue;
         if (sp > 1 && (k_blocks < 16 * sp || t >= sm_count)) continue;
         const int kbs = ceil_div(k_blocks, sp);
         if (sp > 1 && kbs % kpb) continue;   // a stage must not straddle two splits
@@ -324,7 +326,9 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   DeviceState &dev = device_state();
   const int eb = a.int8 ? 1 : 2;
   const int out_bytes = a.out_kind == OUT_BF16 ? 2 : 4;
-  MatmulConfig cfg = a.force ? *a.force : select_matmul_config(a.M, a.N, a.K, eb, out_bytes, dev.sm_count);
+  // partial sums that leave through peer stores are not split along K here: choose the tile knowing that
+  const int max_splits = (a.n_peers > 0) ? 1 : 8;
+  MatmulConfig cfg = a.force ? *a.force : select_matmul_config(a.M, a.N, a.K, eb, out_bytes, dev.sm_count, max_splits);
   const int64_t ld_out = a.ld_out ? a.ld_out : a.N;
 
   GemmParams p{};
@@ -338,10 +342,6 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   p.out_rows = int(a.M);
   p.out_cols = int(a.N);
   p.error = dev.d_error;
-  {
-    static const int park = [] { const char *e = std::getenv("GC_B200_PARK"); return (e && e[0] == '1') ? 1 : 0; }();
-    p.park_epilogue = park;
-  }
 
   // operand roles in MMA orientation
   const void *pa, *pb;
@@ -397,8 +397,10 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
       throw std::invalid_argument("peer stores need whole 16-byte chunks per row and at most 8 peers");
     if (a.out_kind != OUT_F32 && (a.peer_plane != 0 || a.peer_rows != 0))
       throw std::invalid_argument("planes and row scatter exist for f32 partial sums only");
-    cfg.splits = 1;
-    p.splits = 1;
+    // no K split, except for the row scatter when the caller has sized the owners' buffers for one plane per split
+    const int keep = (a.peer_rows > 0 && a.force && a.peer_splits == cfg.splits) ? cfg.splits : 1;
+    cfg.splits = keep;
+    p.splits = keep;
     if (a.peer_rows > 0 && (a.peer_rows * a.n_peers != a.M)) throw std::invalid_argument("row scatter needs M = peers x rows per peer");
     if (a.peer_multicast && (a.n_peers != 1 || a.peer_rows != 0 || cfg.swapped))
       throw std::invalid_argument("multicast stores take one address, every rank receives everything, row-major form only");
@@ -415,7 +417,7 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
         if (!a.signal_peer[d]) throw std::invalid_argument("null peer counter");
         p.signal_peer[d] = a.signal_peer[d];
       }
-      if (a.arrivals_per_peer) *a.arrivals_per_peer = p.tiles_n * (a.peer_rows / 32);
+      if (a.arrivals_per_peer) *a.arrivals_per_peer = p.tiles_n * (a.peer_rows / 32) * p.splits;
     }
   }
   if (a.wait_counter) {
@@ -424,7 +426,7 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
     p.epoch = a.epoch;
     p.wait_per_step = a.wait_per_step;
   }
-  const bool split = cfg.splits > 1;
+  const bool split = cfg.splits > 1 && a.n_peers == 0;   // (with peers the planes live at the owners)
   void *planes = nullptr;
   if (split) {
     const size_t need = size_t(cfg.splits) * size_t(a.M) * size_t(a.N) * 4;
@@ -463,6 +465,40 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
       p.tmC = make_tmap_3d(ct, p.out, uint64_t(a.N), uint64_t(a.M), uint64_t(std::max(1, p.splits)), uint64_t(p.ld_out) * esz,
                            split ? uint64_t(p.split_stride) * esz : uint64_t(a.M) * uint64_t(p.ld_out) * esz, 128 / esz, 32, 1);
       p.tma_store = 1;
+    }
+  }
+  // Row scatter of f32 partial sums: through the copy engine as well, one tensor map per owner (tile widths that are
+  // whole 32-column slabs; GC_B200_PEER_TMA=0 keeps the register-store form)
+  if (!cfg.swapped && a.n_peers > 0 && a.peer_rows > 0 && a.peer_rows % 32 == 0 && a.out_kind == OUT_F32 && !a.peer_multicast &&
+      p.BN % 32 == 0 && a.N % 4 == 0) {
+    static const bool on = [] { const char *e = std::getenv("GC_B200_PEER_TMA"); return !(e && e[0] == '0'); }();
+    bool ok = on;
+    for (int d = 0; d < a.n_peers && ok; ++d) ok = tma_compatible(a.peer_out[d], a.N, 4);
+    if (ok) {
+      const uint64_t planes = uint64_t(a.n_peers) * uint64_t(p.splits);
+      for (int d = 0; d < a.n_peers; ++d)
+        p.tmPeer[d] = make_tmap_3d(ElemType::F32, a.peer_out[d], uint64_t(a.N), uint64_t(a.peer_rows), planes, uint64_t(a.N) * 4,
+                                   uint64_t(a.peer_rows) * uint64_t(a.N) * 4, 32, 32, 1);
+      p.tma_store = 1;
+      p.tma_peer = 1;
+    }
+  }
+  // All-gather of C through the copy engine: every finished slab is stored once per rank from shared memory (one
+  // cp.async.bulk.tensor store per rank and slab instead of a loop of 16-byte stores per thread and rank)
+  if (!cfg.swapped && a.n_peers > 0 && a.peer_rows == 0 && !a.peer_multicast && p.acc_dump == nullptr && p.splits == 1 &&
+      (a.out_kind == OUT_BF16 || a.out_kind == OUT_DEQUANT_F32)) {
+    static const bool on = [] { const char *e = std::getenv("GC_B200_PEER_TMA"); return !(e && e[0] == '0'); }();
+    const int esz = a.out_kind == OUT_BF16 ? 2 : 4;
+    const bool plain = a.out_kind == OUT_BF16 ? (a.bias_kind == BIAS_NONE || a.bias_kind == BIAS_BF16) : (a.bias_kind == BIAS_NONE || a.bias_kind == BIAS_F32);
+    bool ok = on && plain && p.BN % (128 / esz) == 0;
+    for (int d = 0; d < a.n_peers && ok; ++d) ok = tma_compatible(a.peer_out[d], ld_out, esz);
+    if (ok) {
+      const ElemType ct = a.out_kind == OUT_BF16 ? ElemType::BF16 : ElemType::F32;
+      for (int d = 0; d < a.n_peers; ++d)
+        p.tmPeer[d] = make_tmap_3d(ct, a.peer_out[d], uint64_t(a.N), uint64_t(a.M), 1, uint64_t(ld_out) * esz,
+                                   uint64_t(a.M) * uint64_t(ld_out) * esz, 128 / esz, 32, 1);
+      p.tma_store = 1;
+      p.tma_peer = 2;
     }
   }
   const int units = p.tiles_m * p.tiles_n * p.splits;
@@ -554,10 +590,18 @@ reduce_planes_bf16x4_kernel(const float4 *parts, int nparts, long long plane4, u
   pdl_launch_dependents();
   pdl_wait();   // the planes come from the kernel ahead in the stream
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    // four planes' loads in flight before the first add (additions stay in split order)
     float4 s = parts[i];
-    for (int k = 1; k < nparts; ++k) {
-      const float4 t = parts[(long long)k * plane4 + i];
-      s.x = __fadd_rn(s.x, t.x); s.y = __fadd_rn(s.y, t.y); s.z = __fadd_rn(s.z, t.z); s.w = __fadd_rn(s.w, t.w);
+    for (int k = 1; k < nparts; k += 4) {
+      float4 t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (k + u < nparts) t[u] = parts[(long long)(k + u) * plane4 + i];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (k + u < nparts) {
+          s.x = __fadd_rn(s.x, t[u].x); s.y = __fadd_rn(s.y, t[u].y); s.z = __fadd_rn(s.z, t[u].z); s.w = __fadd_rn(s.w, t[u].w);
+        }
     }
     uint32_t lo = pack_bf16x2_rn(s.x, s.y), hi = pack_bf16x2_rn(s.z, s.w);
     if (bias) {

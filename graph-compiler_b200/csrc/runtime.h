@@ -64,9 +64,11 @@ struct MatmulConfig {
   int kpb;       // K blocks of 128 bytes per pipeline stage (0 or 1: one)
 };
 // dtype_bytes: 2 (bf16) or 1 (int8).  out_bytes: bytes per output element written by the GEMM kernel.
-MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
+// max_splits < 8 restricts the K split (1: none - launches whose partial sums leave through peer stores); such a
+// request is answered by the model alone.
+MatmulConfig select_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count, int max_splits = 8);
 // The fitted time model alone (select_matmul_config consults the measured configurations of tune_cache.h first).
-MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
+MatmulConfig model_matmul_config(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count, int max_splits = 8);
 // Bytes of f32 / s32 split-K partial planes the selected configuration of this shape needs (0: no split).
 size_t matmul_scratch_bytes(int64_t M, int64_t N, int64_t K, int dtype_bytes, int out_bytes, int sm_count);
 // Whether the TMA path can take this operand layout (16-byte aligned base and row pitch).
@@ -100,6 +102,8 @@ struct MatmulArgs {
   int n_peers = 0;              // > 0: push the f32 result into plane `peer_plane` of each peer buffer
   int peer_plane = 0;
   int peer_rows = 0;            // > 0: rows are scattered to their owner (row / peer_rows) instead of sent to every peer
+  int peer_splits = 1;          // row scatter only: K splits of this launch, each with its own plane at the owner
+                                // (plane = peer_plane * peer_splits + split; the owner's buffer holds n_peers * peer_splits planes)
   void *const *peer_out = nullptr;
   int peer_multicast = 0;       // 1: n_peers == 1 and peer_out[0] is an NVLink multicast address of all ranks' buffers
   const MatmulConfig *force = nullptr; // optional override

@@ -58,31 +58,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
 }
 
-// Wait of a warp that has nothing else to do for a long time (an epilogue warp waiting for a whole
-// main loop): the suspend-time hint lets the hardware park the thread instead of re-issuing the
-// poll, which keeps issue slots and the shared-memory pipe free for the producer and MMA threads.
-__device__ __forceinline__ bool mbar_test_parked(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(20000u)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity) {
-  if (mbar_test(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_test_parked(bar, parity)) return true;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
-  }
-}
-
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -354,6 +329,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p) {
 }
 __device__ __forceinline__ void red_release_sys_add_u32(uint32_t *p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Release by ONE thread on behalf of a group: the other threads' stores are ordered before this call by the barrier
+// the group has just passed (bar.sync / bar.warp.sync), and release semantics are cumulative over what
+// happened-before, so one acq_rel fence and one release add publish the whole group's stores - instead of a
+// sequentially consistent system fence in every thread, which costs tens of microseconds when stores to another
+// GPU are still on their way.
+__device__ __forceinline__ void publish_and_count(uint32_t *counter, uint32_t n = 1u) {
+  red_release_sys_add_u32(counter, n);   // the release of the add is the one system-scope fence (measured: ~8 us per
+                                         // kernel for every further one when hundreds of CTAs execute it)
+}
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ void red_relaxed_sys_add_u32(uint32_t *p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Bounded wait until *p has reached `target`.  Returns false on time-out (the caller records an error code and
 // leaves through its normal tear-down).  The sleep keeps the poll off the issue slots of the working warps.

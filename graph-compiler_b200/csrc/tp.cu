@@ -63,7 +63,7 @@ struct PeerCopy {
 // the planes in rank order (every row is reduced exactly once, so all ranks end with identical bits), one cast,
 // bias, second cast, ReLU (the reference's epilogue order), store the bf16 rows into every rank's activation
 // buffer, then count this CTA in at every rank.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 tp_reduce_bcast_kernel(const float4 *parts, int nparts, long long plane4, long long total4, int n4, const uint2 *bias, int relu,
                        PeerRows peers, int n_peers, long long dst4, const uint32_t *part_landed, uint32_t per_step,
                        const uint32_t *step, int *error) {
@@ -78,10 +78,19 @@ tp_reduce_bcast_kernel(const float4 *parts, int nparts, long long plane4, long l
   __syncthreads();
   if (ok) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
-      float4 s = __ldcg(parts + i);   // written by other GPUs: read through L2
-      for (int k = 1; k < nparts; ++k) {
-        const float4 t = __ldcg(parts + (long long)k * plane4 + i);
-        s.x = __fadd_rn(s.x, t.x); s.y = __fadd_rn(s.y, t.y); s.z = __fadd_rn(s.z, t.z); s.w = __fadd_rn(s.w, t.w);
+      // planes are read four at a time (all four loads in flight before the first add: the additions stay in plane
+      // order, the load latencies overlap); written by other GPUs, so read through L2
+      float4 s = __ldcg(parts + i);
+      for (int k = 1; k < nparts; k += 4) {
+        float4 t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (k + u < nparts) t[u] = __ldcg(parts + (long long)(k + u) * plane4 + i);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (k + u < nparts) {
+            s.x = __fadd_rn(s.x, t[u].x); s.y = __fadd_rn(s.y, t[u].y); s.z = __fadd_rn(s.z, t[u].z); s.w = __fadd_rn(s.w, t[u].w);
+          }
       }
       uint32_t lo = pack_bf16x2_rn(s.x, s.y), hi = pack_bf16x2_rn(s.z, s.w);
       if (bias) {
@@ -97,9 +106,11 @@ tp_reduce_bcast_kernel(const float4 *parts, int nparts, long long plane4, long l
     }
   }
   // counted in even after a time-out, so that the other ranks' waits end (the error word tells the host)
-  __threadfence_system();
   __syncthreads();
-  if (int(threadIdx.x) < n_peers) red_release_sys_add_u32(peers.landed[threadIdx.x], 1u);
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();   // ONE system-scope fence per CTA publishes the whole CTA's stores (cumulative over the barrier)
+    for (int d = 0; d < n_peers; ++d) red_relaxed_sys_add_u32(peers.landed[d], 1u);
+  }
 }
 
 // Last kernel of a step: the result is complete on this rank once every owner's rows have landed; then the step
@@ -126,9 +137,11 @@ tp_scatter_rows_kernel(const uint4 *src, long long n16, PeerCopy peers, int n_pe
     for (int d = 0; d < n_peers; ++d)
       if (d != self) peers.dst[d][i] = v;
   }
-  __threadfence_system();
   __syncthreads();
-  if (int(threadIdx.x) < n_peers) red_release_sys_add_u32(peers.landed[threadIdx.x], 1u);
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    for (int d = 0; d < n_peers; ++d) red_relaxed_sys_add_u32(peers.landed[d], 1u);
+  }
 }
 
 // Wait self-test (failure path): a kernel that waits, with a caller-given short limit, on a counter nobody adds
@@ -154,8 +167,9 @@ void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t st
 
 int reduce_blocks(int64_t rows, int64_t N) {
   // a function of the shape alone: every rank must expect the same number of arrivals
+  // (CTAs of 1024 threads, at most 148: every CTA ends with one system-scope fence, so few large CTAs beat many small ones)
   const long long total4 = rows * N / 4;
-  return int(std::max<long long>(1, std::min<long long>((total4 + 255) / 256, 592)));
+  return int(std::max<long long>(1, std::min<long long>((total4 + 1023) / 1024, 148)));
 }
 
 } // namespace
@@ -169,6 +183,7 @@ struct gcb200_tp_mlp {
   std::vector<int64_t> hidden;
   std::vector<const void *> W, B;
   std::vector<void *> recv[2], act[2], x_in;
+  int recv_planes = 0;   // f32 planes of [rows, width] each receive buffer holds (at least `world`)
   std::vector<uint32_t *> sig;
   // local state, created by the first step (create itself needs no device)
   std::mutex mu;
@@ -227,14 +242,26 @@ struct gcb200_tp_mlp {
     row_arrivals.clear();
     for (int x = 0; x < exchanges(); ++x) {
       const int64_t N = hidden[size_t(2 * x + 2)], K = hidden[size_t(2 * x + 1)] / world;
-      MatmulConfig c = select_matmul_config(M, N, K, 2, 4, sm_count);
+      // The K split of these layers is first of all the split across ranks.  Where a rank's share of K is still long
+      // and 256 x 256 tiles leave SMs idle, the rank splits its share once more: every (rank, split) owns a plane at
+      // the row owner (twice the partial-sum bytes over NVLink, so only while the GEMM is long enough to hide them).
+      MatmulConfig c = select_matmul_config(M, N, K, 2, 4, sm_count, /*max_splits=*/1);
       if (c.swapped) throw std::logic_error("tensor-parallel layers need a batch of more than 64 rows");
-      c.splits = 1;   // the K split of these layers is the split across ranks
+      c.splits = 1;
       c.pair = 0;
+      const int k_blocks = int((K + 63) / 64);
+      if (M % 256 == 0 && N % 256 == 0 && M <= 1024 && k_blocks >= 32) {
+        const int pair_tiles = int(M / 256) * int(N / 256);
+        c.pair = 1;
+        c.bn = 256;
+        c.kpb = 1;
+        c.stages = 6;
+        if (recv_planes >= 2 * world && 4 * pair_tiles <= sm_count && k_blocks >= 64) c.splits = 2;
+      }
       const int tiles_n = int((N + c.bn - 1) / c.bn);
-      c.grid = std::min(int((M + 127) / 128) * tiles_n, sm_count);
+      c.grid = std::min(int((M + 127) / 128) * tiles_n * c.splits, sm_count);
       row_cfg.push_back(c);
-      row_arrivals.push_back(tiles_n * int(rows() / 32));
+      row_arrivals.push_back(tiles_n * int(rows() / 32) * c.splits);
     }
   }
 
@@ -298,6 +325,7 @@ struct gcb200_tp_mlp {
         m.n_peers = world; m.peer_plane = rank; m.peer_out = bufs; m.peer_rows = int(rows());
         m.signal_peer = sigs;
         m.force = &row_cfg[size_t(e)];
+        m.peer_splits = row_cfg[size_t(e)].splits;
         int arrivals = 0;
         m.arrivals_per_peer = &arrivals;
         matmul_tc(m, s);
@@ -311,8 +339,8 @@ struct gcb200_tp_mlp {
           pr.landed[r] = counter(r, SIG_ROWS0 + e);
         }
         const long long total4 = rows() * Nr / 4;
-        launch_pdl(tp_reduce_bcast_kernel, dim3(unsigned(reduce_blocks(rows(), Nr))), dim3(256), s,
-                   reinterpret_cast<const float4 *>(recv[e & 1][size_t(rank)]), world, total4, total4, int(Nr / 4),
+        launch_pdl(tp_reduce_bcast_kernel, dim3(unsigned(reduce_blocks(rows(), Nr))), dim3(1024), s,
+                   reinterpret_cast<const float4 *>(recv[e & 1][size_t(rank)]), world * row_cfg[size_t(e)].splits, total4, total4, int(Nr / 4),
                    reinterpret_cast<const uint2 *>(B[size_t(2 * e + 1)]), relu, pr, world, (long long)(rank * total4),
                    reinterpret_cast<const uint32_t *>(counter(rank, SIG_PART0 + e)), uint32_t(world * row_arrivals[size_t(e)]), step_word,
                    d.d_error);
@@ -411,6 +439,8 @@ GCB_EXPORT int gcb200_tp_mlp_create(const gcb200_tp_mlp_desc *d, gcb200_tp_mlp *
       throw std::invalid_argument("the batch must be a multiple of 128 and of 32 x the number of ranks (every epilogue warp's rows have one owner)");
     auto t = std::make_unique<gcb200_tp_mlp>();
     t->world = d->world; t->rank = d->rank; t->layers = d->layers; t->relu = d->relu ? 1 : 0; t->M = d->batch;
+    t->recv_planes = d->recv_planes > 0 ? d->recv_planes : d->world;
+    if (t->recv_planes < d->world) throw std::invalid_argument("the receive buffers must hold at least one plane per rank");
     for (int i = 0; i <= d->layers; ++i) {
       const int64_t h = d->hidden[i];
       if (h <= 0 || h % (8 * d->world)) throw std::invalid_argument("every layer width must be a positive multiple of 8 x the number of ranks");
@@ -465,7 +495,8 @@ GCB_EXPORT int gcb200_tp_mlp_describe(const gcb200_tp_mlp *t, int sm_count, char
       os << "layer " << 2 * e << ": column-parallel " << m.M << "x" << Nc << "x" << Kc;
       if (e > 0) os << " waits rows_landed[" << e - 1 << "] += " << m.world * reduce_blocks(m.rows(), m.hidden[size_t(2 * e)]) << " per step";
       os << "\nlayer " << 2 * e + 1 << ": row-parallel " << m.M << "x" << Nr << "x" << Nc << " bn " << m.row_cfg[size_t(e)].bn
-         << " -> part_landed[" << e << "] += " << m.row_arrivals[size_t(e)] << " per rank\n";
+         << (m.row_cfg[size_t(e)].pair ? " on CTA pairs" : "") << " K splits " << m.row_cfg[size_t(e)].splits << " -> part_landed[" << e
+         << "] += " << m.row_arrivals[size_t(e)] << " per rank\n";
       os << "reduce " << e << ": rows " << m.rank * m.rows() << ".." << (m.rank + 1) * m.rows() << " waits part_landed[" << e
          << "] += " << m.world * m.row_arrivals[size_t(e)] << " per step, " << reduce_blocks(m.rows(), Nr) << " CTAs -> rows_landed[" << e
          << "] at every rank, buffers slot " << (e & 1) << "\n";

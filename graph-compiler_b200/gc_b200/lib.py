@@ -37,7 +37,8 @@ class TpMlpDesc(C.Structure):
 
     _fields_ = [("world", _int), ("rank", _int), ("batch", _i64), ("layers", _int), ("hidden", C.POINTER(_i64)),
                 ("weights", C.POINTER(_vp)), ("biases", C.POINTER(_vp)), ("relu", _int),
-                ("recv", C.POINTER(_vp) * 2), ("act", C.POINTER(_vp) * 2), ("signals", C.POINTER(_vp)), ("x_in", C.POINTER(_vp))]
+                ("recv", C.POINTER(_vp) * 2), ("act", C.POINTER(_vp) * 2), ("signals", C.POINTER(_vp)), ("x_in", C.POINTER(_vp)),
+                ("recv_planes", _int)]
 
 
 _lib = None
@@ -342,7 +343,7 @@ class TpMlpPlan:
     (``recv0, recv1, act0, act1, signals`` and optionally ``x_in``), ``weights`` / ``biases`` lists of this rank's
     shard addresses (0 / None = no bias).  Creating and describing a plan needs no device."""
 
-    def __init__(self, world, rank, batch, hidden, weights, biases, relu, recv, act, signals, x_in=None):
+    def __init__(self, world, rank, batch, hidden, weights, biases, relu, recv, act, signals, x_in=None, recv_planes=0):
         layers = len(hidden) - 1
 
         def table(vals):
@@ -360,6 +361,7 @@ class TpMlpPlan:
         d.act[0], d.act[1] = C.cast(k[5], C.POINTER(_vp)), C.cast(k[6], C.POINTER(_vp))
         d.signals = C.cast(k[7], C.POINTER(_vp))
         d.x_in = C.cast(k[8], C.POINTER(_vp)) if x_in else C.POINTER(_vp)()
+        d.recv_planes = recv_planes
         self._h = _vp(None)
         check(load().gcb200_tp_mlp_create(C.byref(d), C.byref(self._h)))
 

@@ -214,7 +214,7 @@ class FusedTensorParallelMLP:
 
         self.recv, self.act, recv_p, act_p = [], [], [], []
         for _ in range(2):
-            t, p = shared((self.world, batch // self.world, nmax), torch.float32)
+            t, p = shared((2 * self.world, batch // self.world, nmax), torch.float32)   # one plane per rank and K split
             self.recv.append(t); recv_p.append(p)
             t, p = shared((batch, nmax), torch.bfloat16)
             self.act.append(t); act_p.append(p)
@@ -226,7 +226,8 @@ class FusedTensorParallelMLP:
         torch.cuda.synchronize()
         dist.barrier(self.group)          # every rank's counters are zero before anyone adds to them
         self.plan = lib.TpMlpPlan(self.world, self.rank, batch, self.hidden, [w.data_ptr() for w in self.w],
-                                  [0 if b is None else b.data_ptr() for b in self.b], relu, recv_p, act_p, sig_p, x_p)
+                                  [0 if b is None else b.data_ptr() for b in self.b], relu, recv_p, act_p, sig_p, x_p,
+                                  recv_planes=2 * self.world)
         self.launches_per_step = 3 * (len(self.w) // 2) + 1
         self.collectives_per_step = 0
         self._slot = (len(self.w) // 2 - 1) & 1

@@ -256,7 +256,7 @@ int gcb200_schedule_memory(const uint64_t *trace_buffer, const uint64_t *trace_s
  *
  * The caller provides the memory every rank can address (e.g. torch symmetric memory), as tables indexed by rank,
  * this rank's own entry included:
- *   recv[s][r]   f32  [world][batch / world][max row-parallel width]   partial sums, s = 0, 1 (consecutive exchanges alternate)
+ *   recv[s][r]   f32  [recv_planes][batch / world][max row-parallel width]   partial sums, s = 0, 1 (consecutive exchanges alternate)
  *   act[s][r]    bf16 [batch][max row-parallel width]                  reduced activations / the result
  *   signals[r]   uint32[16], zeroed once before the first step (all ranks, then a barrier)
  *   x_in[r]      bf16 [batch][hidden[0]]  (optional; needed by gcb200_tp_mlp_execute)
@@ -287,6 +287,8 @@ typedef struct {
   void *const *act[2];
   void *const *signals;
   void *const *x_in;             /* may be NULL */
+  int recv_planes;               /* planes of [batch / world][width] f32 each recv buffer holds; 0 = world.  With 2 x world
+                                    a rank whose share of K is long splits it once more (one plane per rank and split) */
 } gcb200_tp_mlp_desc;
 int gcb200_tp_mlp_create(const gcb200_tp_mlp_desc *desc, gcb200_tp_mlp **plan);
 int gcb200_tp_mlp_destroy(gcb200_tp_mlp *plan);

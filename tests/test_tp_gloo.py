@@ -177,3 +177,39 @@ def test_column_sharded_gemms_and_head_sharded_attention(world):
     for r in range(world):
         for got, w in zip(res[r], want):
             assert np.array_equal(got, w), r      # every rank holds the full result, identical to one device
+
+
+def test_fused_plan_counters_agree_across_ranks():
+    """The tensor-parallel plan behind the C ABI (gcb200_tp_mlp_create / _describe; host only): what every owner's
+    reduction waits for per step equals what all ranks' row-parallel GEMMs add to its counter, what the next layer
+    waits for equals what all owners' reductions add, for 2, 4 and 8 ranks of BASELINE configs[2]; bad shapes are
+    refused with a clear message."""
+    import re
+
+    from gc_b200 import lib
+
+    hidden = [4096, 16384, 4096, 16384, 4096]
+    for world in (2, 4, 8):
+        fake = lambda base: [base + 0x100000 * i for i in range(world)]
+        texts = []
+        for rank in range(world):
+            plan = lib.TpMlpPlan(world, rank, 512, hidden, [0x1000, 0x2000, 0x3000, 0x4000], [0x5000, 0x5100, 0x5200, 0x5300], True,
+                                 [fake(0x10000000), fake(0x20000000)], [fake(0x30000000), fake(0x40000000)], fake(0x50000000), fake(0x60000000))
+            texts.append(plan.describe(148))
+            plan.destroy()
+        for x in range(2):
+            adds = [int(re.search(rf"part_landed\[{x}\] \+= (\d+) per rank", t).group(1)) for t in texts]
+            waits = [int(re.search(rf"waits part_landed\[{x}\] \+= (\d+) per step", t).group(1)) for t in texts]
+            assert len(set(adds)) == 1 and all(w == sum(adds) for w in waits)
+            ctas = [int(re.search(rf"reduce {x}: .*?, (\d+) CTAs", t).group(1)) for t in texts]
+            assert len(set(ctas)) == 1
+            if x == 0:
+                nxt = [int(re.search(r"waits rows_landed\[0\] \+= (\d+) per step", t).group(1)) for t in texts]
+                assert all(n == sum(ctas) for n in nxt)
+        rows = [re.search(r"rows (\d+)\.\.(\d+)", t).groups() for t in texts]
+        assert [int(a) for a, _ in rows] == [r * 512 // world for r in range(world)]          # every row has exactly one owner
+    with pytest.raises(lib.GcB200Error) as ei:
+        lib.TpMlpPlan(8, 0, 384, hidden, [1] * 4, [0] * 4, True, [[16] * 8, [16] * 8], [[16] * 8, [16] * 8], [16] * 8)
+    assert "multiple of 128" in str(ei.value)
+    with pytest.raises(lib.GcB200Error):
+        lib.TpMlpPlan(3, 0, 384, [4096, 16384, 4096], [1] * 2, [0] * 2, True, [[16] * 3, [16] * 3], [[16] * 3, [16] * 3], [16] * 3)   # 4096 % 24
