@@ -250,13 +250,15 @@ struct gcb200_tp_mlp {
       c.splits = 1;
       c.pair = 0;
       const int k_blocks = int((K + 63) / 64);
-      if (M % 256 == 0 && N % 256 == 0 && M <= 1024 && k_blocks >= 32) {
-        const int pair_tiles = int(M / 256) * int(N / 256);
+      // Measured per rank shape (512 x 4096 x K, single launches): K = 8192: pairs with the extra split 43.7 us against
+      // 47.7 us for 128-wide one-CTA tiles; K = 4096: 31.4 against 29.8 us; K = 2048: 128-wide one-CTA tiles win (21.3 us).
+      const int pair_tiles = int(M / 256) * int(N / 256);
+      if (M % 256 == 0 && N % 256 == 0 && M <= 1024 && k_blocks >= 128 && recv_planes >= 2 * world && 4 * pair_tiles <= sm_count) {
         c.pair = 1;
         c.bn = 256;
         c.kpb = 1;
         c.stages = 6;
-        if (recv_planes >= 2 * world && 4 * pair_tiles <= sm_count && k_blocks >= 64) c.splits = 2;
+        c.splits = 2;
       }
       const int tiles_n = int((N + c.bn - 1) / c.bn);
       c.grid = std::min(int((M + 127) / 128) * tiles_n * c.splits, sm_count);
