@@ -531,6 +531,8 @@ def main():
     ap.add_argument("--flush", default="auto", choices=["auto", "on", "off"],
                     help="--case only: write a 256 MiB buffer between timed launches (auto: when the working set is below 256 MB)")
     a = ap.parse_args()
+    if a.tp_timeline:
+        os.environ["GC_B200_TP_TRACE"] = "1"   # read by the plan's first step
     a.warmup = max(a.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -663,6 +665,16 @@ def main():
                 print(f"tp{world} MLP step, rank 0, last of {len(lines)} eagerly launched steps (microseconds from the end of the "
                       "launch before to the end of this one):")
                 print(lines[-1])
+            # the same step as the bench times it (one CUDA-graph replay per step, back to back), read from the time
+            # stamps the kernels write themselves
+            dist.barrier()
+            for _ in range(max(4, a.warmup)):
+                tpf.step(Xd)
+            torch.cuda.synchronize()
+            trace = tpf.plan.trace()
+            if rank == 0:
+                print(f"tp{world} MLP step, rank 0, last of back-to-back graph replays, device time stamps:")
+                print(trace)
             assert lib.device_error() == 0
             dist.barrier()
             tpf.close()

@@ -92,8 +92,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&bars->tmem_base);
   // the set-up above touched only shared and tensor memory and may overlap the tail of the kernel ahead
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_store(p.trace, 0);
   pdl_launch_dependents();
   pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_store(p.trace, 1);
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -121,6 +123,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!pair_rows_landed(p)) err = ERR_WAIT_PEER;
         fence_proxy_async_global();
         gate_open = true;
+        trace_max(p.trace, 2);
       };
       if (gated && is_a) peer_gate();
       for (int u = pair; u < units && !err; u += pairs) {
@@ -239,6 +242,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace_max(p.trace, 3);
   cluster_sync_all();   // no CTA leaves while its peer may still signal it or read its shared memory
   if (warp == 1) {
     tc_fence_after();

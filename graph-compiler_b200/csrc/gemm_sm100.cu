@@ -101,8 +101,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&bars->tmem_base);
   // Everything above touched only shared and tensor memory and may overlap the tail of the kernel
   // ahead in the stream; from here on operands are read and results written.
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_store(p.trace, 0);
   pdl_launch_dependents();
   pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_store(p.trace, 1);
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------------ TMA producers
@@ -133,6 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!peer_rows_landed(p)) err = ERR_WAIT_PEER;
         fence_proxy_async_global();
         gate_open = true;
+        trace_max(p.trace, 2);
       };
       if (gated && is_act) peer_gate();
       for (int u = blockIdx.x; u < units && !err; u += gridDim.x) {
@@ -275,6 +278,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace_max(p.trace, 3);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);

@@ -81,6 +81,7 @@ struct GemmParams {
   const uint32_t *epoch;
   uint32_t wait_per_step;
   int *error;           // device int, set to an ErrCode on a bounded-wait time-out
+  unsigned long long *trace;   // optional time stamps of this launch (sm100_ptx.cuh: trace_store / trace_max)
   // TMA-store epilogue (one-CTA kernel, row-major orientation): tmC covers the output as
   // [planes][rows][cols] with a box of {128 bytes of columns, 32 rows, 1}; each epilogue warp hands its
   // 32 x 128-byte slabs to the copy engine instead of storing them itself.

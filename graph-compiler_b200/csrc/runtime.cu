@@ -342,6 +342,7 @@ void matmul_tc(const MatmulArgs &a, cudaStream_t stream) {
   p.out_rows = int(a.M);
   p.out_cols = int(a.N);
   p.error = dev.d_error;
+  p.trace = a.trace;
 
   // operand roles in MMA orientation
   const void *pa, *pb;

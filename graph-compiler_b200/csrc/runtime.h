@@ -115,6 +115,7 @@ struct MatmulArgs {
   const uint32_t *epoch = nullptr;          // required with wait_counter
   uint32_t wait_per_step = 0;
   int *arrivals_per_peer = nullptr;         // out: counter increments each peer receives from this launch
+  unsigned long long *trace = nullptr;      // optional device time stamps of this launch (four words, see sm100_ptx.cuh)
 };
 void matmul_tc(const MatmulArgs &a, cudaStream_t stream);
 

@@ -317,6 +317,22 @@ __device__ __forceinline__ void multimem_st_16(void *mc_addr, uint4 v) {
                : "memory");
 }
 
+// Optional device-side time stamps of a kernel (nanoseconds of %globaltimer), four words per launch slot:
+//  [0] CTA 0 started, [1] CTA 0 was released by the kernel ahead (griddepcontrol.wait returned),
+//  [2] latest "cross-GPU wait satisfied" over all CTAs, [3] latest CTA end.  [0] and [1] are plain stores, [2] and [3]
+// maxima: the timer only grows, so a slot needs no reset between the steps of a replayed graph.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_store(unsigned long long *trace, int word) {
+  if (trace != nullptr) trace[word] = global_timer_ns();
+}
+__device__ __forceinline__ void trace_max(unsigned long long *trace, int word) {
+  if (trace != nullptr) atomicMax(trace + word, global_timer_ns());
+}
+
 // ----------------------------------------------------------------------------- cross-GPU hand-off
 // Monotonic counters in peer-mapped device memory order work between kernels on different GPUs without a
 // host round trip: a producer stores its data (plain stores, possibly to a peer), fences at system scope and

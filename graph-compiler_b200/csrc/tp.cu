@@ -23,6 +23,7 @@
 // because each of its layers needs rows from that peer's previous reduction; receive and activation buffers
 // alternate between consecutive exchanges.
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -66,14 +67,17 @@ struct PeerCopy {
 __global__ void __launch_bounds__(1024)
 tp_reduce_bcast_kernel(const float4 *parts, int nparts, long long plane4, long long total4, int n4, const uint2 *bias, int relu,
                        PeerRows peers, int n_peers, long long dst4, const uint32_t *part_landed, uint32_t per_step,
-                       const uint32_t *step, int *error) {
+                       const uint32_t *step, int *error, unsigned long long *trace) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_store(trace, 0);
   pdl_launch_dependents();
   pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_store(trace, 1);
   __shared__ int ok;
   if (threadIdx.x == 0) {
     const uint32_t target = (*reinterpret_cast<const volatile uint32_t *>(step) + 1u) * per_step;
     ok = wait_counter_reached(part_landed, target, 4 * WAIT_LIMIT_CYCLES) ? 1 : 0;
     if (!ok) atomicExch(error, ERR_WAIT_PEER);
+    trace_max(trace, 2);
   }
   __syncthreads();
   if (ok) {
@@ -110,19 +114,25 @@ tp_reduce_bcast_kernel(const float4 *parts, int nparts, long long plane4, long l
   if (threadIdx.x == 0) {
     fence_acq_rel_sys();   // ONE system-scope fence per CTA publishes the whole CTA's stores (cumulative over the barrier)
     for (int d = 0; d < n_peers; ++d) red_relaxed_sys_add_u32(peers.landed[d], 1u);
+    trace_max(trace, 3);
   }
 }
 
 // Last kernel of a step: the result is complete on this rank once every owner's rows have landed; then the step
 // word moves on (plain store: the kernels of the next step come later in the same stream).
-__global__ void tp_step_end_kernel(const uint32_t *rows_landed, uint32_t per_step, uint32_t *step, uint32_t *xstep, int *error) {
+__global__ void tp_step_end_kernel(const uint32_t *rows_landed, uint32_t per_step, uint32_t *step, uint32_t *xstep, int *error,
+                                   unsigned long long *trace) {
+  if (threadIdx.x == 0) trace_store(trace, 0);
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x == 0) {
+    trace_store(trace, 1);
     const uint32_t n = *reinterpret_cast<volatile uint32_t *>(step);
     if (!wait_counter_reached(rows_landed, (n + 1u) * per_step, 4 * WAIT_LIMIT_CYCLES)) atomicExch(error, ERR_WAIT_PEER);
+    trace_max(trace, 2);
     *reinterpret_cast<volatile uint32_t *>(step) = n + 1u;
     if (xstep) *reinterpret_cast<volatile uint32_t *>(xstep) = *reinterpret_cast<volatile uint32_t *>(xstep) + 1u;
+    trace_max(trace, 3);
   }
 }
 
@@ -199,6 +209,10 @@ struct gcb200_tp_mlp {
   std::vector<std::string> mark_names;
   size_t marks_used = 0;
   bool timeline = false;
+  // optional device-side time stamps (GC_B200_TP_TRACE=1 when the plan takes its first step): four words per kernel of a
+  // step, written by the kernels themselves, so that a replayed graph can be read as well (see gcb200_tp_mlp_trace)
+  unsigned long long *trace = nullptr;
+  std::vector<std::string> trace_names;
   std::vector<MatmulConfig> row_cfg;   // configuration of every row-parallel layer (fixes the arrival counts)
   std::vector<int> row_arrivals;
   struct Graph {
@@ -233,6 +247,7 @@ struct gcb200_tp_mlp {
     for (void *p : col_out)
       if (p) cudaFree(p);
     if (splitk) cudaFree(splitk);
+    if (trace) cudaFree(trace);
     if (stream) cudaStreamDestroy(stream);
     if (host_code) cudaFreeHost(host_code);
   }
@@ -284,6 +299,11 @@ struct gcb200_tp_mlp {
       GCB_CUDA(cudaMalloc(&splitk, need));
       splitk_bytes = need;
     }
+    if (const char *e = std::getenv("GC_B200_TP_TRACE"); e && e[0] == '1') {
+      const size_t words = size_t(4) * size_t(3 * exchanges() + 1);
+      GCB_CUDA(cudaMalloc(reinterpret_cast<void **>(&trace), words * sizeof(unsigned long long)));
+      GCB_CUDA(cudaMemset(trace, 0, words * sizeof(unsigned long long)));
+    }
     GCB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     GCB_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&host_code), sizeof(int), cudaHostAllocDefault));
     *host_code = 0;
@@ -297,6 +317,12 @@ struct gcb200_tp_mlp {
     const void *h = x;
     marks_used = 0;
     mark("start", s);
+    trace_names.clear();
+    auto slot = [&](const std::string &name) -> unsigned long long * {
+      if (!trace) return nullptr;
+      trace_names.push_back(name);
+      return trace + 4 * (trace_names.size() - 1);
+    };
     for (int e = 0; e < exchanges(); ++e) {
       const int64_t Kc = hidden[size_t(2 * e)], Nc = hidden[size_t(2 * e + 1)] / world, Nr = hidden[size_t(2 * e + 2)];
       {   // column-parallel layer: local bias / ReLU; its input rows come from the other ranks (except the first layer's)
@@ -314,6 +340,7 @@ struct gcb200_tp_mlp {
           m.wait_per_step = uint32_t(world * scatter_blocks());
           m.epoch = counter(rank, SIG_XSTEP);
         }
+        m.trace = slot("column-parallel gemm " + std::to_string(2 * e));
         matmul_tc(m, s);
         mark("column-parallel gemm (+ wait for the previous exchange's rows)", s);
       }
@@ -330,6 +357,7 @@ struct gcb200_tp_mlp {
         m.peer_splits = row_cfg[size_t(e)].splits;
         int arrivals = 0;
         m.arrivals_per_peer = &arrivals;
+        m.trace = slot("row-parallel gemm " + std::to_string(2 * e + 1) + " + row scatter");
         matmul_tc(m, s);
         if (arrivals != row_arrivals[size_t(e)]) throw std::logic_error("row-parallel layer ran with an unplanned tile configuration");
         mark("row-parallel gemm + row scatter to the owners", s);
@@ -345,7 +373,7 @@ struct gcb200_tp_mlp {
                    reinterpret_cast<const float4 *>(recv[e & 1][size_t(rank)]), world * row_cfg[size_t(e)].splits, total4, total4, int(Nr / 4),
                    reinterpret_cast<const uint2 *>(B[size_t(2 * e + 1)]), relu, pr, world, (long long)(rank * total4),
                    reinterpret_cast<const uint32_t *>(counter(rank, SIG_PART0 + e)), uint32_t(world * row_arrivals[size_t(e)]), step_word,
-                   d.d_error);
+                   d.d_error, slot("reduce " + std::to_string(e) + " + all-gather stores"));
         mark("wait for all ranks' partial sums + reduce + all-gather stores", s);
       }
       h = act[e & 1][size_t(rank)];
@@ -353,7 +381,7 @@ struct gcb200_tp_mlp {
     const int last = exchanges() - 1;
     launch_pdl(tp_step_end_kernel, dim3(1), dim3(32), s, reinterpret_cast<const uint32_t *>(counter(rank, SIG_ROWS0 + last)),
                uint32_t(world * reduce_blocks(rows(), hidden.back())), counter(rank, SIG_STEP),
-               x_scattered ? counter(rank, SIG_XSTEP) : static_cast<uint32_t *>(nullptr), d.d_error);
+               x_scattered ? counter(rank, SIG_XSTEP) : static_cast<uint32_t *>(nullptr), d.d_error, slot("end of step"));
     mark("wait for every owner's rows (end of step)", s);
   }
 
@@ -587,6 +615,38 @@ GCB_EXPORT int gcb200_tp_mlp_timeline(gcb200_tp_mlp *t, const void *x, void *str
     float total = 0.f;
     if (t->marks_used > 1) GCB_CUDA(cudaEventElapsedTime(&total, t->marks[0], t->marks[t->marks_used - 1]));
     os << total * 1e3f << " us  whole step (eager launches; a replayed graph has no launch gaps)\n";
+    const std::string str = os.str();
+    if (needed) *needed = str.size() + 1;
+    if (buf && cap) {
+      const size_t n = std::min(cap - 1, str.size());
+      std::memcpy(buf, str.data(), n);
+      buf[n] = '\0';
+    }
+    return GCB200_OK;
+  } catch (...) {
+    return guard_status(std::current_exception());
+  }
+}
+
+GCB_EXPORT int gcb200_tp_mlp_trace(gcb200_tp_mlp *t, char *buf, size_t cap, size_t *needed) {
+  try {
+    if (!t) throw std::invalid_argument("null plan");
+    std::lock_guard<std::mutex> g(t->mu);
+    if (!t->ready || !t->trace || t->trace_names.empty())
+      throw std::invalid_argument("no time stamps: set GC_B200_TP_TRACE=1 before the plan's first step, and take a step");
+    GCB_CUDA(cudaDeviceSynchronize());
+    std::vector<unsigned long long> w(4 * t->trace_names.size());
+    GCB_CUDA(cudaMemcpy(w.data(), t->trace, w.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    std::ostringstream os;
+    os << "us after the first kernel of the step started: launched, released by the kernel ahead, cross-GPU wait over, last CTA done\n";
+    const unsigned long long t0 = w[0];
+    auto us = [&](unsigned long long v) { return v ? double((long long)(v - t0)) * 1e-3 : -1.0; };
+    char line[256];
+    for (size_t k = 0; k < t->trace_names.size(); ++k) {
+      std::snprintf(line, sizeof line, "%8.1f %8.1f %8.1f %8.1f  %s\n", us(w[4 * k]), us(w[4 * k + 1]), us(w[4 * k + 2]), us(w[4 * k + 3]),
+                    t->trace_names[k].c_str());
+      os << line;
+    }
     const std::string str = os.str();
     if (needed) *needed = str.size() + 1;
     if (buf && cap) {

@@ -89,6 +89,7 @@ def load() -> C.CDLL:
         "gcb200_tp_mlp_step": [_vp, _vp, _vp, C.POINTER(_vp)],
         "gcb200_tp_mlp_execute": [_vp, _vp, _vp],
         "gcb200_tp_mlp_timeline": [_vp, _vp, _vp, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)],
+        "gcb200_tp_mlp_trace": [_vp, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)],
         "gcb200_wait_selftest": [C.c_longlong, _vp],
     }
     for name, argtypes in sig.items():
@@ -382,6 +383,12 @@ class TpMlpPlan:
         """One eagerly launched step with an event behind every launch: one line per kernel, microseconds first."""
         buf = C.create_string_buffer(4096)
         check(load().gcb200_tp_mlp_timeline(self._h, _vp(x_ptr), _stream() if stream is None else _vp(stream), buf, 4096, None))
+        return buf.value.decode()
+
+    def trace(self) -> str:
+        """Device-side time stamps of the most recent step (needs GC_B200_TP_TRACE=1 before the first step)."""
+        buf = C.create_string_buffer(4096)
+        check(load().gcb200_tp_mlp_trace(self._h, buf, 4096, None))
         return buf.value.decode()
 
     def execute(self, x_host_ptr: int, y_host_ptr: int = 0):

@@ -299,6 +299,11 @@ int gcb200_tp_mlp_execute(gcb200_tp_mlp *plan, const void *x_host, void *y_host)
  * <what>": the time from the end of the launch before to the end of this one, waits for other ranks included) and
  * the total.  Synchronises `stream`.  Every rank must call it (it is a step like any other). */
 int gcb200_tp_mlp_timeline(gcb200_tp_mlp *plan, const void *x, void *stream, char *buf, size_t cap, size_t *needed);
+/* Device-side time stamps of the plan's most recent step, written by the kernels themselves (so a replayed CUDA graph can
+ * be read, which events cannot see into): one line per kernel with four times in microseconds after the step's first
+ * kernel started - launched, released by the kernel ahead in the stream, cross-GPU wait over, last CTA done.  Only for a
+ * plan whose first step ran with GC_B200_TP_TRACE=1 in the environment (an error otherwise).  Synchronises the device. */
+int gcb200_tp_mlp_trace(gcb200_tp_mlp *plan, char *buf, size_t cap, size_t *needed);
 
 /* Failure-path self-test: launches a kernel that waits (for at most `limit_cycles` SM clock cycles, which must not
  * exceed the library's own limit) on a counter nothing ever adds to, gives up, records code 7 in the device error
