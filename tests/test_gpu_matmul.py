@@ -138,6 +138,35 @@ def test_matmul_u8s8_bit_exact(M, N, K):
     assert np.array_equal(acc_only.cpu().numpy(), wacc)
 
 
+def test_matmul_u8s8_on_cta_pairs_bit_exact():
+    """The CTA-pair kernel on u8 x s8 (the selector's choice for several waves of tiles, forced here on a small shape
+    through the measured-configuration cache): s32 accumulators and dequantised output bit-identical to the oracle."""
+    M, N, K = 512, 1024, 2048
+    g = torch.Generator().manual_seed(77)
+    A = torch.randint(0, 256, (M, K), generator=g, dtype=torch.uint8)
+    W = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8)
+    scale = torch.rand(N, generator=g) * 0.009 + 0.001
+    bias = torch.rand(N, generator=g) * 2 - 1
+    Wd = W.to(DEV)
+    comp = lib.colsum_s8(Wd, 128)
+    saved = lib.tune_cache_get(M, N, K, 1, 4)
+    try:
+        lib.tune_cache_put(M, N, K, lib.MatmulConfig(0, 256, 1, 8, 8, 0, 1, 1), 1, 4)
+        out, acc = lib.matmul_u8s8(A.to(DEV), Wd, scale.to(DEV), bias.to(DEV), comp, want_acc=True)
+        out_tma, _ = lib.matmul_u8s8(A.to(DEV), Wd, scale.to(DEV), bias.to(DEV), comp)   # copy-engine epilogue
+        torch.cuda.synchronize()
+        _no_device_error()
+    finally:
+        if saved is not None:
+            lib.tune_cache_put(M, N, K, saved, 1, 4)
+        else:
+            lib.tune_cache_erase(M, N, K, 1, 4)
+    wacc, wout = oracle.linear_u8s8(A.numpy(), W.numpy(), scale.numpy(), bias.numpy(), zp_a=128)
+    assert np.array_equal(acc.cpu().numpy(), wacc)
+    assert np.array_equal(out.cpu().numpy(), wout)
+    assert np.array_equal(out_tma.cpu().numpy(), wout)
+
+
 def test_matmul_f32_capi_case():
     """test/dnnl/TestApiOps.cpp:69-119 values."""
     A = (torch.arange(128)[:, None] + torch.arange(512)[None, :]).float()
