@@ -475,11 +475,14 @@ struct dnnl_graph_compiler_executable {
         piped_in_host = t->data;
       } else {
         DeviceBuffer &b = in_stage[i];
-        const bool resident = lt.constant && b.cached_host == t->data && b.bytes >= bytes;
+        // GC_B200_CONST_CACHE=0: re-read constant tensors on every call, as the reference does (for callers that
+        // rewrite a weight buffer in place)
+        static const bool const_cache = [] { const char *e = std::getenv("GC_B200_CONST_CACHE"); return !(e && e[0] == '0'); }();
+        const bool resident = const_cache && lt.constant && b.cached_host == t->data && b.bytes >= bytes;
         if (!resident) {
           b.reserve(bytes);
           GCB_CUDA(cudaMemcpyAsync(b.ptr, t->data, bytes, cudaMemcpyHostToDevice, s));
-          b.cached_host = lt.constant ? t->data : nullptr;
+          b.cached_host = (const_cache && lt.constant) ? t->data : nullptr;
           // column sums depend on the weights alone: only those computed from THIS argument are stale now
           for (const Step &qs : plan.steps)
             if (qs.kind == StepKind::QMATMUL && qs.scratch_slot >= 0) {

@@ -194,6 +194,39 @@ def test_quantized_matmul_partition_bit_exact():
         assert np.array_equal(acc, wacc) and np.array_equal(out, wout)
 
 
+def test_constant_tensors_are_cached_by_address_unless_switched_off():
+    """A `property_type: constant` weight rewritten IN PLACE between two calls: resident (old) weights by default - the
+    documented contract - and fresh weights with GC_B200_CONST_CACHE=0, as the reference re-reads them.  The switch is
+    read once per process, so each setting runs in a process of its own."""
+    import os
+    import subprocess
+    import sys
+
+    code = r'''
+import json, sys, numpy as np
+from gc_b200 import api
+M, N, K = 128, 64, 128
+t = lambda i, s, c=False: dict({"id": i, "dtype": "f32", "shape": s}, **({"property_type": "constant"} if c else {}))
+js = json.dumps({"version": "3.5.0", "engine_kind": "cpu", "fpmath_mode": "strict", "graph": [
+    {"kind": "MatMul", "inputs": [t(0, [M, K]), t(1, [K, N], True)], "outputs": [t(2, [M, N])]}]})
+exe = api.GraphCompiler().compile(js)
+A = np.ones((M, K), np.float32); W = np.ones((K, N), np.float32); out = np.empty((M, N), np.float32)
+exe.execute({0: A, 1: W}, {2: out}); first = float(out[0, 0])
+W *= 2.0
+exe.execute({0: A, 1: W}, {2: out}); second = float(out[0, 0])
+print(first, second)
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    got = {}
+    for switch in ("1", "0"):
+        env = dict(os.environ, GC_B200_CONST_CACHE=switch, PYTHONPATH=os.path.join(root, "graph-compiler_b200"))
+        r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        got[switch] = tuple(float(x) for x in r.stdout.split()[-2:])
+    assert got["1"] == (128.0, 128.0)   # cached by address: the rewritten buffer is not read again
+    assert got["0"] == (128.0, 256.0)
+
+
 def test_quantized_matmul_keeps_its_column_sums_across_calls_and_steps():
     """Device activations, constant host weights, and two temporaries after the matmul: the second call skips the
     column-sum kernel (the weights are resident), so the sums must have survived the first call's later steps."""
