@@ -25,9 +25,12 @@
  *   - tensor `data` may be a HOST pointer (as in the reference; copied to and from
  *     the device by the call) or a DEVICE pointer (used in place, zero copy; the
  *     call first waits for all work previously queued on the device, on any stream);
- *   - the JSON may carry the extension op kinds documented in INTEGRATION.md
- *     (int8 matmul with per-channel dequantisation, fused attention), which the
- *     reference's front end cannot express;
+ *   - the JSON may carry op kinds which the reference's front end cannot express:
+ *     `QuantizedMatMul` (src u8 [M,K], weights s8 [K,N], scales f32 [N], optional bias
+ *     f32 [N]; attr `src_zp` s64, optional `relu`; dst f32 [M,N] =
+ *     float(acc - src_zp * colsum(W)) * scale + bias, optionally the raw s32 sums as a
+ *     second output), `SDPA` (Q, K, V bf16 [B,H,S,128]; attrs `scale` f32, `causal`
+ *     bool; O bf16), and `StaticReshape`, `Exp`, `Negate`;
  *   - `engine_kind` "gpu" is accepted besides "cpu".
  */
 #ifndef DNNL_GRAPH_COMPILER_H
