@@ -213,3 +213,10 @@ def test_fused_plan_counters_agree_across_ranks():
     assert "multiple of 128" in str(ei.value)
     with pytest.raises(lib.GcB200Error):
         lib.TpMlpPlan(3, 0, 384, [4096, 16384, 4096], [1] * 2, [0] * 2, True, [[16] * 3, [16] * 3], [[16] * 3, [16] * 3], [16] * 3)   # 4096 % 24
+    # time stamps exist only for a plan that has taken a step with GC_B200_TP_TRACE=1: asking earlier is an argument error
+    # (answered on the host, no device needed)
+    plan = lib.TpMlpPlan(2, 0, 512, hidden, [0x1000] * 4, [0] * 4, True, [[16] * 2, [16] * 2], [[16] * 2, [16] * 2], [16] * 2)
+    with pytest.raises(lib.GcB200Error) as ei:
+        plan.trace()
+    assert "GC_B200_TP_TRACE" in str(ei.value)
+
